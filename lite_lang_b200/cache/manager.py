@@ -70,8 +70,23 @@ class PagedGroupSpec:
     window: Optional[int]
     planes: int                 # cache planes (one per run-step that writes into this group)
     value_head_dim: Optional[int] = None   # width of a value; None: head_dim; 0: the group has no value plane
+    chunk: Optional[int] = None            # a token reads positions of its own chunk of this many only
 
     kind = "paged"
+
+    @property
+    def releases(self) -> bool:
+        """Whether pages go back while the request lives (a window or chunks bound what a token reads)."""
+        return self.window is not None or self.chunk is not None
+
+    def first_needed(self, length: int) -> int:
+        """The first position that the token at position ``length`` (the next one) reads."""
+        first = 0
+        if self.window is not None:
+            first = max(first, length - self.window + 1)
+        if self.chunk is not None:
+            first = max(first, (length // self.chunk) * self.chunk)
+        return first
 
     @property
     def value_dim(self) -> int:
@@ -82,9 +97,10 @@ class PagedGroupSpec:
         ``step_tokens`` a step: all of them without a window; with one, the window, the step's new tokens
         (pages are given back after the step) and the partly used pages at both ends."""
         full = (length + page_size - 1) // page_size
-        if self.window is None:
+        if not self.releases:
             return full
-        return min(full, (self.window + step_tokens + page_size - 1) // page_size + 1)
+        reach = min(x for x in (self.window, self.chunk) if x is not None)
+        return min(full, (reach + step_tokens + page_size - 1) // page_size + 1)
 
 
 @dataclass(frozen=True)
@@ -203,7 +219,7 @@ class CacheManager:
         Groups that keep every position set it; if every group has a window, the number of requests
         whose windows fit, times the longest request."""
         full = [self.allocators[g].num_pages * self.page_size for g in self.paged_ids
-                if self.groups[g].window is None]
+                if not self.groups[g].releases]
         if full:
             return min(full)
         if not self.paged_ids:
@@ -255,12 +271,11 @@ class CacheManager:
         req.length = new_length
         self.lengths[slot] = new_length
         for g in self.paged_ids:
-            w = self.groups[g].window
-            if w is None:
+            if not self.groups[g].releases:
                 continue
-            # the next token sits at position new_length and reads positions > new_length - w
-            first_needed = max(0, new_length - w + 1)
-            first_live_page = first_needed // self.page_size
+            # the next token sits at position new_length and reads positions > new_length - window, or from the
+            # start of its chunk
+            first_live_page = self.groups[g].first_needed(new_length) // self.page_size
             if first_live_page > req.first_live[g]:
                 gone = []
                 for lp in range(req.first_live[g], min(first_live_page, len(req.pages[g]))):

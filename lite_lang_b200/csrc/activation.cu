@@ -147,3 +147,68 @@ extern "C" int ll_softcap(float* z, long total, float cap, cudaStream_t stream) 
   ll_launch(softcap_kernel, dim3(blocks), dim3(256), 0, stream, z, total, cap);
   return LL_LAUNCH_RESULT();
 }
+
+// ---------------------------------------------------------------------------------------------------------
+// Activation of a plain (ungated) feed-forward, in place: x <- act(x), float32, rounded once.
+// act 0: gelu in its tanh form, 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))); 1: ReLU; 2: SiLU.
+// ---------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float row_activation(float z, int act) {
+  if (act == 1) return fmaxf(z, 0.f);
+  if (act == 2) return z / (1.0f + expf(-z));
+  return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+template <typename T>
+__global__ void act_rows_kernel(T* __restrict__ x, long total, int act) {
+  LL_PDL_TRIGGER();
+  LL_PDL_WAIT();
+  const long step = (long)gridDim.x * blockDim.x;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step)
+    x[i] = from_f32<T>(row_activation(to_f32<T>(x[i]), act));
+}
+
+// 8 bf16 values a thread (total % 8 == 0, 16-byte aligned)
+__global__ void act_rows_bf16x8_kernel(bf16* __restrict__ x, long total8, int act) {
+  LL_PDL_TRIGGER();
+  LL_PDL_WAIT();
+  const long step = (long)gridDim.x * blockDim.x;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total8; i += step) {
+    uint4 v = reinterpret_cast<uint4*>(x)[i];
+    __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 f = __bfloat1622float2(p[k]);
+      p[k] = __floats2bfloat162_rn(row_activation(f.x, act), row_activation(f.y, act));
+    }
+    reinterpret_cast<uint4*>(x)[i] = v;
+  }
+}
+
+extern "C" int ll_act_rows(int dtype, void* x, long total, int act, cudaStream_t stream) {
+  if (total <= 0) return 0;
+  if (act < 0 || act > 2) return (int)cudaErrorInvalidValue;
+  const long most = (long)silu_device_sms() * 16;
+  if (dtype == LL_DTYPE_BF16 && (total % 8) == 0 && ((uintptr_t)x % 16) == 0) {
+    const int blocks = (int)min((total / 8 + 255) / 256, most);
+    ll_launch(act_rows_bf16x8_kernel, dim3(blocks), dim3(256), 0, stream, (bf16*)x, total / 8, act);
+    return LL_LAUNCH_RESULT();
+  }
+  const int blocks = (int)min((total + 255) / 256, most);
+  LL_DISPATCH_DTYPE(dtype, ll_launch(act_rows_kernel<T>, dim3(blocks), dim3(256), 0, stream, (T*)x, total, act));
+  return LL_LAUNCH_RESULT();
+}
+
+// z <- z * factor on float32 logits, in place.
+__global__ void scale_f32_kernel(float* __restrict__ z, long total, float factor) {
+  LL_PDL_TRIGGER();
+  LL_PDL_WAIT();
+  const long step = (long)gridDim.x * blockDim.x;
+  for (long idx = (long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += step) z[idx] *= factor;
+}
+
+extern "C" int ll_scale_f32(float* z, long total, float factor, cudaStream_t stream) {
+  if (total <= 0) return 0;
+  const int blocks = (int)min((total + 255) / 256, (long)silu_device_sms() * 16);
+  ll_launch(scale_f32_kernel, dim3(blocks), dim3(256), 0, stream, z, total, factor);
+  return LL_LAUNCH_RESULT();
+}

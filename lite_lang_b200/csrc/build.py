@@ -48,6 +48,7 @@ LIBRARIES: Dict[str, Tuple[Tuple[str, ...], Tuple[str, ...]]] = {
     "moe": (("moe.cu",), ()),
     "streams": (("streams.cu",), ()),
     "linear_attn": (("linear_attention.cu",), ()),
+    "attn_mod": (("qkv_norm_rotate_store.cu", "attention_modulated.cu"), ()),
 }
 
 _INCLUDE = re.compile(r'^\s*#\s*include\s+"([^"]+)"', re.M)

@@ -72,3 +72,84 @@ extern "C" int ll_add_layernorm(int dtype, void* out, float* residual, const voi
   });
   return LL_LAUNCH_RESULT();
 }
+
+// ---------------------------------------------------------------------------------------------------------
+// Layer norm on a sublayer's *output*, added into a float32 residual stream:
+//
+//   residual += (y - mean(y)) / sqrt(var(y) + eps) * w          (float32, written back unrounded)
+//   copy      = residual rounded to T                           (what the next sublayer's products read)
+//
+// y comes as T [tokens, hidden], or as float32 partial sums [parts, tokens, hidden] of a product that was
+// split over its inner dimension; those are added up in a fixed order and not rounded.  `copy` may be null
+// (float32 storage: the next reader takes the residual itself).  One block a row, two passes over the row
+// in shared memory (mean, then deviations).
+// ---------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void layernorm_into_residual_kernel(T* __restrict__ copy, float* __restrict__ residual,
+                                               const T* __restrict__ y, const float* __restrict__ partial, int parts,
+                                               long part_stride, const float* __restrict__ w, float eps, int hidden) {
+  extern __shared__ float row[];
+  __shared__ float scratch[32];
+  LL_PDL_TRIGGER();
+  LL_PDL_WAIT();
+  const int r = blockIdx.x;
+  float* res = residual + (size_t)r * hidden;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float v;
+    if (partial) {
+      v = 0.f;
+      for (int q = 0; q < parts; ++q) v += partial[(size_t)q * part_stride + (size_t)r * hidden + i];
+    } else {
+      v = to_f32<T>(y[(size_t)r * hidden + i]);
+    }
+    row[i] = v;
+    s += v;
+  }
+  const float mean = block_sum(s, scratch) / (float)hidden;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float c = row[i] - mean;
+    ss += c * c;
+  }
+  const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)hidden + eps);
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float v = res[i] + (row[i] - mean) * inv * w[i];
+    res[i] = v;
+    if (copy) copy[(size_t)r * hidden + i] = from_f32<T>(v);
+  }
+}
+
+// copy: [tokens, hidden] of T or null; residual: float32 [tokens, hidden]; y: T [tokens, hidden] or null when
+// `partial` (float32 [parts, tokens, hidden], part_stride = tokens * hidden) is given.
+extern "C" int ll_layernorm_into_residual(int dtype, void* copy, float* residual, const void* y, const float* partial,
+                                          int parts, long part_stride, const float* w, float eps, int tokens,
+                                          int hidden, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (hidden <= 0 || (y == nullptr) == (partial == nullptr)) return (int)cudaErrorInvalidValue;
+  const size_t smem = sizeof(float) * (size_t)hidden;
+  const int threads = hidden >= 2048 ? 512 : hidden >= 512 ? 256 : 128;
+  LL_DISPATCH_DTYPE(dtype, {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(layernorm_into_residual_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    ll_launch(layernorm_into_residual_kernel<T>, dim3(tokens), dim3(threads), smem, stream, (T*)copy, residual,
+              (const T*)y, partial, parts, part_stride, w, eps, hidden);
+  });
+  return LL_LAUNCH_RESULT();
+}
+
+// copy[t, i] = residual[t, i] rounded to T: the float32 residual stream as the operand of a product.
+template <typename T>
+__global__ void round_rows_kernel(T* __restrict__ copy, const float* __restrict__ x, long total) {
+  LL_PDL_TRIGGER();
+  LL_PDL_WAIT();
+  const long step = (long)gridDim.x * blockDim.x;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += step) copy[i] = from_f32<T>(x[i]);
+}
+
+extern "C" int ll_round_rows(int dtype, void* copy, const float* x, long total, cudaStream_t stream) {
+  if (total <= 0) return 0;
+  const int blocks = (int)min((total + 255) / 256, (long)148 * 16);
+  LL_DISPATCH_DTYPE(dtype, ll_launch(round_rows_kernel<T>, dim3(blocks), dim3(256), 0, stream, (T*)copy, x, total));
+  return LL_LAUNCH_RESULT();
+}

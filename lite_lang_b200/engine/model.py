@@ -127,7 +127,7 @@ class CausalLM:
         for need, n in zip(keys, planes):
             if isinstance(need, PagedKVNeed):
                 vd = need.head_dim if need.value_head_dim is None else need.value_head_dim
-                groups.append(PagedGroupSpec(need.num_kv_heads, need.head_dim, need.window, n, vd))
+                groups.append(PagedGroupSpec(need.num_kv_heads, need.head_dim, need.window, n, vd, need.chunk))
             elif isinstance(need, StateNeed):
                 groups.append(StateGroupSpec(tuple(need.shape), need.dtype, n))
             else:
@@ -161,7 +161,7 @@ class CausalLM:
             part.load(lambda rel, _p=prefix: fetch(_p + rel), dtype, device)
         tied = getattr(self.head, "tied_to", None)
         if tied is not None:
-            if tied != self.embedding.prefix + "weight":
+            if tied != self.embedding.prefix + getattr(self.embedding, "tensor", "weight"):
                 raise ValueError(f"the head is tied to {tied}, which is not the embedding table")
             self.head.tie(self.embedding.weight)
         for b in self.blocks:

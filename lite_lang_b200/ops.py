@@ -1493,3 +1493,144 @@ def linear_attn_out(y: torch.Tensor, o: torch.Tensor, weight: torch.Tensor, gate
     load_library("linear_attn").call("ll_linear_attn_out", c_int(_dtype_code(y)), _ptr(y), _ptr(o), _ptr(weight),
                                      _ptr(gate), c_long(gate.stride(0)), c_float(eps), c_int(n), c_int(width),
                                      _stream())
+
+
+# --------------------------------------------------------------------------
+# a norm on the sublayer's output, a plain feed-forward's activation, scaled logits
+# --------------------------------------------------------------------------
+def layernorm_into_residual(residual: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float,
+                            copy: Optional[torch.Tensor]) -> None:
+    """residual (float32) += layer norm of y times ``weight``; ``copy`` (optional) receives the new residual rows
+    rounded to its dtype.  ``y`` is [tokens, hidden] of the engine's dtype or float32 partial sums
+    [parts, tokens, hidden] of a product split over its inner dimension (added up unrounded)."""
+    _need_cuda(residual, y, weight, copy)
+    _f32(residual, "residual")
+    _f32(weight, "norm weight")
+    n, hidden = residual.shape
+    _need(weight.numel() == hidden, "layernorm_into_residual: weight size")
+    _need(copy is None or (copy.is_contiguous() and tuple(copy.shape) == (n, hidden)),
+          "layernorm_into_residual: copy shape")
+    if y.dim() == 3:
+        _need(y.dtype == torch.float32 and y.is_contiguous() and tuple(y.shape[1:]) == (n, hidden),
+              "layernorm_into_residual: partial sums are float32 [parts, tokens, hidden]")
+        dt = _dtype_code(copy) if copy is not None else 0
+        core().call("ll_layernorm_into_residual", c_int(dt), _ptr(copy), _ptr(residual), c_void_p(0), _ptr(y),
+                    c_int(y.shape[0]), c_long(n * hidden), _ptr(weight), c_float(eps), c_int(n), c_int(hidden),
+                    _stream())
+        return
+    _need(y.is_contiguous() and tuple(y.shape) == (n, hidden) and (copy is None or copy.dtype == y.dtype),
+          "layernorm_into_residual: y is [tokens, hidden] of the copy's dtype")
+    core().call("ll_layernorm_into_residual", c_int(_dtype_code(y)), _ptr(copy), _ptr(residual), _ptr(y), c_void_p(0),
+                c_int(0), c_long(0), _ptr(weight), c_float(eps), c_int(n), c_int(hidden), _stream())
+
+
+def round_rows(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """A float32 residual stream rounded to ``dtype``, as a product's operand (float32: the rows themselves)."""
+    _need_cuda(x)
+    _f32(x, "x")
+    if dtype == torch.float32:
+        return x
+    out = torch.empty(x.shape, dtype=dtype, device=x.device)
+    core().call("ll_round_rows", c_int(_dtype_code(out)), _ptr(out), _ptr(x), c_long(x.numel()), _stream())
+    return out
+
+
+ROW_ACT = {"gelu_tanh": 0, "relu": 1, "silu": 2}
+
+
+def act_rows(x: torch.Tensor, act: str) -> None:
+    """x <- act(x) in place (float32 arithmetic, one rounding): the activation of a feed-forward without a gate."""
+    _need_cuda(x)
+    _need(x.is_contiguous(), "act_rows: x must be contiguous")
+    core().call("ll_act_rows", c_int(_dtype_code(x)), _ptr(x), c_long(x.numel()), c_int(ROW_ACT[act]), _stream())
+
+
+def scale_logits(logits: torch.Tensor, factor: float) -> None:
+    """logits <- logits * factor in place (float32)."""
+    _need_cuda(logits)
+    _f32(logits, "logits")
+    core().call("ll_scale_f32", _ptr(logits), c_long(logits.numel()), c_float(factor), _stream())
+
+
+# --------------------------------------------------------------------------
+# attention with normalised q, k, v and shaped scores
+# --------------------------------------------------------------------------
+QK_NORM = {None: 0, "none": 0, "head_unit": 1, "projection": 2}
+ATTN_MASK = {"causal": 0, "window": 1, "chunk": 2}
+
+
+def qkv_norm_rotate_store(qkv: torch.Tensor, bias: Optional[torch.Tensor], positions: torch.Tensor,
+                          freq: Optional[torch.Tensor], amplitude: float, interleaved: bool, num_heads: int,
+                          num_kv_heads: int, head_dim: int, value_head_dim: int, qk_norm: Optional[str],
+                          q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], value_norm: bool,
+                          eps: float, slot_map: Optional[torch.Tensor], k_cache: Optional[torch.Tensor],
+                          v_cache: Optional[torch.Tensor], page_size: int, status: Optional[torch.Tensor]) -> None:
+    """Bias, the norms of q, k and v (``qk_norm``: "projection": an RMS norm with weights over all of q and all of
+    k before the rotation; "head_unit": every head divided by its root mean square after it; ``value_norm``: the
+    same for every value head), the rotation by angles made in the kernel (cos and sin times ``amplitude``), and
+    the store of k and v.  In place on the first (nh + nkv) * head_dim + nkv * value_head_dim columns of ``qkv``."""
+    _need_cuda(qkv, bias, positions, freq, q_weight, k_weight, slot_map, k_cache, v_cache)
+    for t, nm in ((bias, "bias"), (freq, "freq"), (q_weight, "q norm weight"), (k_weight, "k norm weight")):
+        _f32(t, nm)
+    _i32(positions, "positions")
+    _i32(slot_map, "slot_map")
+    width = (num_heads + num_kv_heads) * head_dim + num_kv_heads * value_head_dim
+    _need(qkv.dim() == 2 and qkv.shape[1] >= width and qkv.stride(1) == 1, "qkv must be [tokens, >= (nh+nkv)*hd + nkv*vd]")
+    _need(bias is None or bias.numel() == width, "bias size")
+    mode = QK_NORM[qk_norm]
+    if mode == 2:
+        _need(q_weight is not None and q_weight.numel() == num_heads * head_dim and k_weight is not None
+              and k_weight.numel() == num_kv_heads * head_dim, "projection norm: weights over all of q and all of k")
+    rot_dim = 0 if freq is None else 2 * freq.numel()
+    _need(rot_dim <= head_dim, "rotation: rot_dim <= head_dim")
+    num_slots = 0
+    if slot_map is not None:
+        _need(k_cache is not None and v_cache is not None, "store needs the cache plane")
+        _need(k_cache.dtype == qkv.dtype and v_cache.dtype == qkv.dtype, "cache dtype differs from activations")
+        _need(k_cache.is_contiguous() and v_cache.is_contiguous(), "cache plane must be contiguous")
+        _need(tuple(k_cache.shape[1:]) == (num_kv_heads, page_size, head_dim)
+              and tuple(v_cache.shape[1:]) == (num_kv_heads, page_size, value_head_dim), "cache plane shape")
+        num_slots = k_cache.shape[0] * page_size
+    load_library("attn_mod").call(
+        "ll_qkv_norm_rotate_store", c_int(_dtype_code(qkv)), _ptr(qkv), c_long(qkv.stride(0)), _ptr(bias),
+        _ptr(positions), _ptr(freq), c_int(rot_dim), c_float(amplitude), c_int(1 if interleaved else 0),
+        c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(value_head_dim), c_int(mode), _ptr(q_weight),
+        _ptr(k_weight), c_int(1 if value_norm else 0), c_float(eps), _ptr(slot_map), _ptr(k_cache), _ptr(v_cache),
+        c_int(page_size), c_long(num_slots), c_int(qkv.shape[0]), _ptr(status), _stream())
+
+
+def attention_modulated(out: torch.Tensor, q: torch.Tensor, q_stride: int, gate: Optional[torch.Tensor],
+                        k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
+                        token_req: torch.Tensor, req_slot: torch.Tensor, positions: torch.Tensor, num_tokens: int,
+                        num_heads: int, num_kv_heads: int, head_dim: int, value_head_dim: int, page_size: int,
+                        mask: str, mask_size: Optional[int], sink: bool, scale: float,
+                        temperature: Optional[torch.Tensor], head_mix: Optional[torch.Tensor],
+                        status: Optional[torch.Tensor]) -> None:
+    """Attention of every new token over its request's cached keys with shaped scores (any sizes, both dtypes):
+    a number a head on the scores (``temperature``), the heads' scores mixed by ``head_mix`` [nh, nh], a window
+    or chunks (``mask``, ``mask_size``), one more key of score 0 without a value (``sink``), a sigmoid gate a
+    head on the output (``gate``: a view whose element [t, h] is token t's gate input of head h, with the row
+    stride of ``q``)."""
+    _need_cuda(out, q, gate, k_cache, v_cache, block_table, token_req, req_slot, positions, temperature, head_mix)
+    for t, nm in ((block_table, "block_table"), (token_req, "token_req"), (req_slot, "req_slot"),
+                  (positions, "positions")):
+        _i32(t, nm)
+    _f32(temperature, "temperature")
+    _f32(head_mix, "head_mix")
+    _need(num_heads % num_kv_heads == 0, "num_heads must be a multiple of num_kv_heads")
+    _need(out.dtype == q.dtype == k_cache.dtype == v_cache.dtype, "attention: dtypes differ")
+    _need(out.stride(1) == 1 and out.shape[1] == num_heads * value_head_dim, "attention: out shape")
+    _need(k_cache.is_contiguous() and v_cache.is_contiguous(), "cache plane must be contiguous")
+    _need(tuple(k_cache.shape[1:]) == (num_kv_heads, page_size, head_dim)
+          and tuple(v_cache.shape[1:]) == (num_kv_heads, page_size, value_head_dim), "cache plane shape")
+    _need(temperature is None or temperature.numel() == num_heads, "temperature: a number a head")
+    _need(head_mix is None or tuple(head_mix.shape) == (num_heads, num_heads), "head_mix is [heads, heads]")
+    _need(gate is None or (gate.dtype == q.dtype and gate.stride(0) == q_stride and gate.stride(1) == 1),
+          "gate: a view of the projection's rows")
+    load_library("attn_mod").call(
+        "ll_attention_modulated", c_int(_dtype_code(out)), _ptr(out), c_long(out.stride(0)), _ptr(q), c_long(q_stride),
+        _ptr(gate), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), c_int(block_table.stride(0)), _ptr(token_req),
+        _ptr(req_slot), _ptr(positions), c_int(num_tokens), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim),
+        c_int(value_head_dim), c_int(page_size), c_int(k_cache.shape[0]), c_int(ATTN_MASK[mask]),
+        c_int(int(mask_size or 0)), c_int(1 if sink else 0), c_float(scale), _ptr(temperature), _ptr(head_mix),
+        _ptr(status), _stream())

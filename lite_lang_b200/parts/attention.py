@@ -45,6 +45,8 @@ class GQAttention(Mixer):
         pos = p.get("position")
         self.position = build_part("position", pos) if pos is not None else None
         self.computed_rotation = bool(getattr(self.position, "computed", False))
+        if getattr(self.position, "amplitude", 1.0) != 1.0:
+            raise ValueError("gqa_attention: a rotation with an amplitude goes with modulated_attention")
         if self.vdim != self.head_dim and self.position is not None and not self.computed_rotation:
             raise ValueError("gqa_attention: values wider or narrower than keys go with a position part that makes "
                              "its angles in the kernel (or none)")

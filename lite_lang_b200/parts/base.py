@@ -66,6 +66,8 @@ class PagedKVNeed:
     head_dim: int                          # width of a key
     window: Optional[int] = None           # None: every earlier position stays readable
     value_head_dim: Optional[int] = None   # width of a value; None: head_dim; 0: no value plane
+    # a token reads the positions of its own chunk only (chunks of this many positions, counted from 0)
+    chunk: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -116,6 +118,8 @@ class Norm(Part):
         norm's output hands their outputs on as a tuple; they are added to each other first, then
         to the residual.
         """
+        if isinstance(delta, ResidualCopy):
+            delta = None
         if isinstance(delta, (tuple, list)):
             parts = [whole_output(d, residual.dtype).float() for d in delta if d is not None]
             delta = None
@@ -195,6 +199,13 @@ class StreamWrite(NamedTuple):
     y: torch.Tensor           # [tokens, hidden] in the engine's dtype, or float32 partial sums [parts, tokens, hidden]
     mix: torch.Tensor         # float32 [streams, streams]: row = the stream read, column = the stream written
     write: torch.Tensor       # float32 [streams]
+
+
+class ResidualCopy(NamedTuple):
+    """Handed on by a block in the place of a pending output when nothing is pending: the float32 residual rows,
+    already summed, rounded to the engine's dtype (what the next block's products read, made in the pass that
+    wrote the residual).  A norm that is given one has nothing to add."""
+    rows: torch.Tensor        # [tokens, hidden] in the engine's dtype
 
 
 class Connection(Part):

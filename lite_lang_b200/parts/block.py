@@ -9,7 +9,8 @@ two), which is why a block hands its last, not yet added, output on as ``delta``
 
 from __future__ import annotations
 
-from .base import Block, NormEntry, NormSplit, register_part
+from .. import ops
+from .base import Block, NormEntry, NormSplit, ResidualCopy, register_part
 
 
 class PreNormBlock(Block):
@@ -61,6 +62,41 @@ class ParallelMixerOnlyBlock(Block):
         return h, self.mixer.forward(x, step, caches["mixer"])
 
 
+class OutputNormBlock(Block):
+    """Norm on the sublayers' outputs: h += norm(mixer(h)); h += norm(feed_forward(h)).  The sublayers read the
+    float32 residual stream itself, rounded to the engine's dtype; that copy is made by the norm's pass over the
+    residual and handed on to the next block in the place of a pending output (``ResidualCopy``)."""
+
+    roles = {"mixer": "mixer", "mixer_norm": "norm", "feed_forward": "feed_forward", "feed_forward_norm": "norm"}
+
+    @staticmethod
+    def _operand(h, delta, dtype):
+        if isinstance(delta, ResidualCopy):
+            return delta.rows
+        if delta is not None:
+            raise TypeError("a block with norms on its sublayers' outputs cannot take a pending output")
+        return ops.round_rows(h, dtype)
+
+    def forward(self, h, delta, step, caches):
+        x = self._operand(h, delta, self.mixer_norm.out_dtype)
+        x = self.mixer_norm.add_into(h, self.mixer.forward(x, step, caches["mixer"]))
+        x = self.feed_forward_norm.add_into(h, self.feed_forward.forward(x, step))
+        return h, ResidualCopy(x)
+
+
+class OutputNormMixerOnlyBlock(OutputNormBlock):
+    """The same arrangement for a layer without a feed-forward: h += norm(mixer(h))."""
+
+    roles = {"mixer": "mixer", "mixer_norm": "norm"}
+
+    def forward(self, h, delta, step, caches):
+        x = self._operand(h, delta, self.mixer_norm.out_dtype)
+        x = self.mixer_norm.add_into(h, self.mixer.forward(x, step, caches["mixer"]))
+        return h, ResidualCopy(x)
+
+
 register_part("block", "pre_norm", PreNormBlock)
+register_part("block", "output_norm", OutputNormBlock)
+register_part("block", "output_norm_mixer_only", OutputNormMixerOnlyBlock)
 register_part("block", "parallel", ParallelBlock)
 register_part("block", "parallel_mixer_only", ParallelMixerOnlyBlock)

@@ -75,6 +75,8 @@ class LMHead(Part):
         # ``softcap`` c: logits <- c * tanh(logits / c)
         cap = spec.params.get("softcap")
         self.softcap = float(cap) if cap else None
+        # ``scale``: a constant on the logits (applied to the float32 product)
+        self.scale = float(spec.params.get("scale", 1.0))
         self.weight: Optional[torch.Tensor] = None
 
     def tensors(self) -> Dict[str, TensorDecl]:
@@ -90,6 +92,8 @@ class LMHead(Part):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         logits = ops.linear(x, self.weight, out_dtype=torch.float32)
+        if self.scale != 1.0:
+            ops.scale_logits(logits, self.scale)
         if self.softcap is not None:
             ops.softcap(logits, self.softcap)
         return logits

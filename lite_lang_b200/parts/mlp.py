@@ -71,4 +71,42 @@ class GatedMLP(FeedForward):
         return ops.linear(act, self.w_down, partial_ok=True)
 
 
+class DenseMLP(FeedForward):
+    """Feed-forward without a gate: down(act(up(x))), no biases; ``activation`` gelu_tanh (the tanh form of
+    GELU), relu or silu, evaluated in float32.  ``tensor_names``: (up, down) under the prefix."""
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.hidden_size = int(spec.params["hidden_size"])
+        self.intermediate_size = int(spec.params["intermediate_size"])
+        act = spec.params.get("activation", "gelu_tanh")
+        if act not in ops.ROW_ACT:
+            raise ValueError(f"dense_mlp: activation {act!r} is not built ({', '.join(ops.ROW_ACT)})")
+        self.activation = act
+        self.names = tuple(spec.params.get("tensor_names") or ("up_proj.weight", "down_proj.weight"))
+        self.w_up = None
+        self.w_down = None
+
+    def tensors(self) -> Dict[str, TensorDecl]:
+        h, i = self.hidden_size, self.intermediate_size
+        return {self.names[0]: TensorDecl((i, h)), self.names[1]: TensorDecl((h, i))}
+
+    def load(self, fetch, dtype, device) -> None:
+        self.w_up = fetch(self.names[0]).to(dtype).to(device).contiguous()
+        self.w_down = fetch(self.names[1]).to(dtype).to(device).contiguous()
+
+    def kernel_libraries(self):
+        bf16 = self.w_down is not None and self.w_down.dtype == torch.bfloat16
+        return ["core", "gemm_smallm", "gemm_stream", "gemm_tc"] if bf16 else ["core"]
+
+    def weight_bytes(self) -> int:
+        return self.w_up.numel() * self.w_up.element_size() + self.w_down.numel() * self.w_down.element_size()
+
+    def forward(self, x, step):
+        act = ops.linear(x, self.w_up)
+        ops.act_rows(act, self.activation)
+        return ops.linear(act, self.w_down, partial_ok=True)
+
+
 register_part("feed_forward", "gated_mlp", GatedMLP)
+register_part("feed_forward", "dense_mlp", DenseMLP)

@@ -1,0 +1,164 @@
+"""Grouped-query attention over the paged cache with normalised operands and shaped scores.
+
+One part, every mechanism a parameter, so that a design picks the ones it has:
+
+``qkv_bias``          biases on q, k and v, added in the projection
+``qk_norm``           None; "projection": q as one vector of all its heads (and k alike) through an RMS norm
+                      with weights before the rotation; "head_unit": every q and k head divided by its root
+                      mean square after the rotation
+``value_norm``        every value head divided by its root mean square; the cache holds it so
+``position``          a ``rope_computed`` part (partial rotation, interleaved or half-split pairs, scaled
+                      frequencies with an amplitude on cos and sin)
+``scale``             on q . k
+``head_temperature``  a number a head on its scores
+``head_mix``          the heads' scores mixed by a matrix [heads, heads] before the softmax: every head's score
+                      of a (query, key) pair becomes a weighted sum of all heads' scores of that pair
+``mask``, ``mask_size``  "causal"; "window": a token sees itself and the mask_size - 1 before it; "chunk": a
+                      token sees the earlier tokens of its own chunk of mask_size positions, chunks counted
+                      from the request's first token
+``sink``              the softmax's denominator gains a 1: one more key of score 0 that carries no value
+``head_gate``         every head's output times sigmoid(w_h . x), x being the input of the projections
+
+The cache holds keys rotated and normalised and values normalised, one plane of pages; with a window or chunks
+the pages that no later token can read go back to the pool while the request lives.  Scores, softmax weights,
+norms and angles are float32 whatever the engine's dtype is.  q | k | v (| gate) are one product.
+"""
+
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from .. import ops
+from ..config.spec import PartSpec
+from .base import Mixer, PagedKVNeed, TensorDecl, build_part, register_part
+
+_NAMES = {"q": "q", "k": "k", "v": "v", "o": "o", "q_bias": "q.b", "k_bias": "k.b", "v_bias": "v.b",
+          "q_norm": "q.norm", "k_norm": "k.norm", "temperature": "temp", "mix": "talk", "gate": "g"}
+
+
+class ModulatedAttention(Mixer):
+    def __init__(self, spec: PartSpec):
+        super().__init__(spec)
+        p = spec.params
+        self.hidden_size = int(p["hidden_size"])
+        self.num_heads = int(p["num_heads"])
+        self.num_kv_heads = int(p["num_kv_heads"])
+        self.head_dim = int(p["head_dim"])
+        self.vdim = int(p.get("value_head_dim") or self.head_dim)
+        self.scale = float(p.get("scale", self.head_dim ** -0.5))
+        self.eps = float(p.get("eps", 1e-6))
+        self.qkv_bias = bool(p.get("qkv_bias", False))
+        self.qk_norm = p.get("qk_norm")
+        self.value_norm = bool(p.get("value_norm", False))
+        self.head_temperature = bool(p.get("head_temperature", False))
+        self.head_mix = bool(p.get("head_mix", False))
+        self.sink = bool(p.get("sink", False))
+        self.head_gate = bool(p.get("head_gate", False))
+        self.mask = str(p.get("mask", "causal"))
+        size = p.get("mask_size")
+        self.mask_size = None if size is None else int(size)
+        if self.num_heads % self.num_kv_heads:
+            raise ValueError("modulated_attention: num_heads must be a multiple of num_kv_heads")
+        if self.qk_norm not in ops.QK_NORM:
+            raise ValueError(f"modulated_attention: qk_norm {self.qk_norm!r}; built: projection, head_unit, None")
+        if self.mask not in ops.ATTN_MASK:
+            raise ValueError(f"modulated_attention: mask {self.mask!r}; built: {', '.join(ops.ATTN_MASK)}")
+        if self.mask != "causal" and (self.mask_size is None or self.mask_size <= 0):
+            raise ValueError(f"modulated_attention: a {self.mask} mask needs a positive mask_size")
+        pos = p.get("position")
+        self.position = build_part("position", pos) if pos is not None else None
+        if self.position is not None and not getattr(self.position, "computed", False):
+            raise ValueError("modulated_attention: the position part must make its angles in the kernel "
+                             "(rope_computed)")
+        self.names = dict(_NAMES)
+        self.names.update(dict(p.get("tensor_names") or {}))
+        self.q_width = self.num_heads * self.head_dim
+        self.k_width = self.num_kv_heads * self.head_dim
+        self.v_width = self.num_kv_heads * self.vdim
+        self.o_width = self.num_heads * self.vdim
+        self.gate_offset = self.q_width + self.k_width + self.v_width
+        self.w_in = self.b_in = self.w_o = None
+        self.q_norm_w = self.k_norm_w = self.temperature = self.mix = None
+
+    def tensors(self) -> Dict[str, TensorDecl]:
+        h, nm = self.hidden_size, self.names
+        d = {nm["q"]: TensorDecl((self.q_width, h)), nm["k"]: TensorDecl((self.k_width, h)),
+             nm["v"]: TensorDecl((self.v_width, h)), nm["o"]: TensorDecl((h, self.o_width))}
+        if self.qkv_bias:
+            d[nm["q_bias"]] = TensorDecl((self.q_width,), "bias")
+            d[nm["k_bias"]] = TensorDecl((self.k_width,), "bias")
+            d[nm["v_bias"]] = TensorDecl((self.v_width,), "bias")
+        if self.qk_norm == "projection":
+            d[nm["q_norm"]] = TensorDecl((self.q_width,), "norm")
+            d[nm["k_norm"]] = TensorDecl((self.k_width,), "norm")
+        if self.head_temperature:
+            d[nm["temperature"]] = TensorDecl((self.num_heads,), "norm")
+        if self.head_mix:
+            d[nm["mix"]] = TensorDecl((self.num_heads, self.num_heads), "bias", std=0.2, eye=1.0)
+        if self.head_gate:
+            d[nm["gate"]] = TensorDecl((self.num_heads, h))
+        return d
+
+    def load(self, fetch, dtype, device) -> None:
+        nm = self.names
+        w = [fetch(nm[r]).to(dtype) for r in (("q", "k", "v", "gate") if self.head_gate else ("q", "k", "v"))]
+        self.w_in = torch.cat(w, dim=0).to(device).contiguous()
+        if self.qkv_bias:
+            b = [fetch(nm[r]).to(torch.float32) for r in ("q_bias", "k_bias", "v_bias")]
+            self.b_in = torch.cat(b, dim=0).to(device).contiguous()
+        self.w_o = fetch(nm["o"]).to(dtype).to(device).contiguous()
+
+        def f32(name):
+            return fetch(nm[name]).to(torch.float32).to(device).contiguous()
+
+        if self.qk_norm == "projection":
+            self.q_norm_w, self.k_norm_w = f32("q_norm"), f32("k_norm")
+        if self.head_temperature:
+            self.temperature = f32("temperature")
+        if self.head_mix:
+            self.mix = f32("mix")
+
+    def weight_bytes(self) -> int:
+        return self.w_in.numel() * self.w_in.element_size() + self.w_o.numel() * self.w_o.element_size()
+
+    def cache_need(self):
+        return PagedKVNeed(self.num_kv_heads, self.head_dim,
+                           self.mask_size if self.mask == "window" else None,
+                           None if self.vdim == self.head_dim else self.vdim,
+                           self.mask_size if self.mask == "chunk" else None)
+
+    def kernel_libraries(self):
+        libs = ["core", "attn_mod"]
+        if self.w_in is not None and self.w_in.dtype == torch.bfloat16:
+            libs.extend(["gemm_smallm", "gemm_stream", "gemm_tc"])
+        return libs
+
+    def prepare(self, device, dtype) -> None:
+        if self.position is not None:
+            self.position.prepare(device)
+
+    # ------------------------------------------------------------------
+    def forward(self, x, step, cache):
+        n = x.shape[0]
+        proj = ops.linear(x, self.w_in)                  # q | k | v (| gate inputs)
+        pos = self.position
+        ops.qkv_norm_rotate_store(
+            proj, self.b_in, step.positions, None if pos is None else pos.freq,
+            1.0 if pos is None else pos.amplitude, bool(pos is None or pos.interleaved), self.num_heads,
+            self.num_kv_heads, self.head_dim, self.vdim, self.qk_norm, self.q_norm_w, self.k_norm_w, self.value_norm,
+            self.eps, cache.slot_map if cache.writable else None, cache.k, cache.v, cache.page_size, step.status)
+        attn = torch.empty((n, self.o_width), dtype=x.dtype, device=x.device)
+        self.attend(attn, proj, step, cache)
+        return ops.linear(attn, self.w_o, partial_ok=self.partial_ok)
+
+    def attend(self, out, proj, step, cache) -> None:
+        gate = proj[:, self.gate_offset:self.gate_offset + self.num_heads] if self.head_gate else None
+        ops.attention_modulated(out, proj, proj.stride(0), gate, cache.k, cache.v, cache.block_table, step.token_req,
+                                step.req_slot, step.positions, proj.shape[0], self.num_heads, self.num_kv_heads,
+                                self.head_dim, self.vdim, cache.page_size, self.mask, self.mask_size, self.sink,
+                                self.scale, self.temperature, self.mix, step.status)
+
+
+register_part("mixer", "modulated_attention", ModulatedAttention)

@@ -12,7 +12,7 @@ from typing import Dict, Optional
 import torch
 
 from .. import ops
-from .base import Norm, StreamWrite, TensorDecl, register_part, whole_output
+from .base import Norm, ResidualCopy, StreamWrite, TensorDecl, register_part, whole_output
 
 
 class RMSNorm(Norm):
@@ -74,6 +74,8 @@ class LayerNormF32Residual(Norm):
     def add_forward(self, residual, delta, rows=None):
         if residual.dtype != torch.float32:
             raise TypeError("layer_norm_f32: the residual stream of this norm is float32")
+        if isinstance(delta, ResidualCopy):      # nothing is pending
+            delta = None
         deltas = [d for d in (delta if isinstance(delta, (tuple, list)) else (delta,)) if d is not None]
         if len(deltas) > 2:
             raise ValueError("layer_norm_f32: at most two pending outputs can be added in the norm")
@@ -146,6 +148,47 @@ class DynamicTanh(Norm):
         return out
 
 
+class OutputLayerNorm(Norm):
+    """Layer norm with a weight and no bias on a sublayer's *output*, which is then added to a float32 residual
+    stream: residual += (y - mean) / sqrt(var + eps) * w.  The sublayers of such a layer read the residual
+    itself, so the pass that writes the residual also leaves it rounded to the engine's dtype for the products
+    that read it next (``add_into`` returns that copy; on the float32 path it is the residual).
+
+    ``y`` may be float32 partial sums [parts, tokens, hidden] of a product split over its inner dimension;
+    they are added up in float32 and not rounded.  ``tensor`` is the weight's name under the prefix.
+    """
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.hidden_size = int(spec.params["hidden_size"])
+        self.eps = float(spec.params["eps"])
+        self.tensor = str(spec.params.get("tensor", "weight"))
+        self.weight: Optional[torch.Tensor] = None
+        self.out_dtype: Optional[torch.dtype] = None
+
+    def tensors(self) -> Dict[str, TensorDecl]:
+        return {self.tensor: TensorDecl((self.hidden_size,), "norm")}
+
+    def load(self, fetch, dtype, device) -> None:
+        self.weight = fetch(self.tensor).to(torch.float32).to(device).contiguous()
+        self.out_dtype = dtype
+
+    def add_into(self, residual: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+        if residual.dtype != torch.float32:
+            raise TypeError("layer_norm_out: the residual stream of this norm is float32")
+        if y.dim() == 2 and y.dtype != self.out_dtype:
+            y = y.to(self.out_dtype)
+        copy = None
+        if self.out_dtype != torch.float32:
+            copy = torch.empty(residual.shape, dtype=self.out_dtype, device=residual.device)
+        ops.layernorm_into_residual(residual, y.contiguous(), self.weight, self.eps, copy)
+        return residual if copy is None else copy
+
+    def forward(self, x, out=None):
+        raise TypeError("layer_norm_out norms a sublayer's output into the residual stream: use add_into")
+
+
 register_part("norm", "rms_norm", RMSNorm)
+register_part("norm", "layer_norm_out", OutputLayerNorm)
 register_part("norm", "dynamic_tanh", DynamicTanh)
 register_part("norm", "layer_norm_f32", LayerNormF32Residual)

@@ -12,6 +12,7 @@ angles are the same numbers on both precisions' paths.
 
 from __future__ import annotations
 
+import math
 from typing import Optional
 
 import torch
@@ -62,7 +63,14 @@ class RotaryComputed(PositionEncoding):
     f_i = theta^(-2i/rotary_dim) / ``position_scale`` (linear scaling of the positions; 1: none), computed in
     float64 on the host and rounded to float32 once.  No table, so no limit on the positions.  ``layout``:
     "interleaved" pairs channel 2i with 2i+1, "half_split" pairs i with i + rotary_dim/2; channels from
-    ``rotary_dim`` on are left as they are.  (u, v) -> (u cos a - v sin a, v cos a + u sin a)."""
+    ``rotary_dim`` on are left as they are.  (u, v) -> (u cos a - v sin a, v cos a + u sin a).
+
+    ``scaling`` (optional: ``factor``, ``original``, ``fast``, ``slow``) stretches the slow frequencies only, so
+    that a model trained on ``original`` positions reaches ``factor`` times as far (YaRN): with
+    d(t) = rotary_dim ln(original / (2 pi t)) / (2 ln theta), lo = max(floor d(fast), 0), hi = min(ceil d(slow),
+    rotary_dim - 1) and r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), pair i turns at
+    f_i / factor * r_i + f_i (1 - r_i); cos and sin are both multiplied by ``amplitude`` = 0.1 ln(factor) + 1
+    (an attention that uses this part reads it and hands it to its kernel)."""
 
     computed = True
     fuses_with_store = False
@@ -79,13 +87,39 @@ class RotaryComputed(PositionEncoding):
             raise ValueError("rope_computed: rotary_dim must be even and position_scale positive")
         self.interleaved = layout == "interleaved"
         self.freq: Optional[torch.Tensor] = None
+        self.amplitude = 1.0
+        sc = spec.params.get("scaling")
+        self.scaling = None
+        if sc:
+            self.scaling = {k: float(sc[k]) for k in ("factor", "original", "fast", "slow")}
+            if self.scaling["factor"] <= 0 or self.scaling["original"] <= 0 or self.theta <= 1.0:
+                raise ValueError("rope_computed: scaling needs a positive factor and original length, theta above 1")
+            self.amplitude = 0.1 * math.log(self.scaling["factor"]) + 1.0
 
-    def prepare(self, device) -> None:
+    def frequencies(self) -> torch.Tensor:
+        """float64 [rotary_dim / 2]: what a position is multiplied by for each pair."""
         i = torch.arange(0, self.rot_dim // 2, dtype=torch.float64)
         f = torch.pow(torch.tensor(self.theta, dtype=torch.float64), -2.0 * i / max(self.rot_dim, 1))
-        self.freq = (f / self.position_scale).to(torch.float32).to(device).contiguous() if self.rot_dim else None
+        f = f / self.position_scale
+        if self.scaling is not None:
+            sc = self.scaling
+
+            def turns(t: float) -> float:
+                return self.rot_dim * math.log(sc["original"] / (2.0 * math.pi * t)) / (2.0 * math.log(self.theta))
+
+            lo = max(math.floor(turns(sc["fast"])), 0)
+            hi = min(math.ceil(turns(sc["slow"])), self.rot_dim - 1)
+            ramp = torch.clamp((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+            f = f / sc["factor"] * ramp + f * (1.0 - ramp)
+        return f
+
+    def prepare(self, device) -> None:
+        self.freq = self.frequencies().to(torch.float32).to(device).contiguous() if self.rot_dim else None
 
     def apply(self, qkv, positions, num_heads, num_kv_heads, head_dim, num_tokens) -> None:
+        if self.amplitude != 1.0:
+            raise ValueError("rope_computed: a scaled rotation's amplitude is applied by the attention part that "
+                             "names it (modulated_attention)")
         ops.bias_rotate_store(qkv[:num_tokens], None, positions, self.freq, self.interleaved, num_heads, num_kv_heads,
                               head_dim, head_dim, None, None, None, 1, None)
 
