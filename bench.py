@@ -457,7 +457,7 @@ def run_ours(args):
 
 
 # ---------------------------------------------------------------------------------------------------------
-# --compare nevurax / redirax: that design beside Qwen2 at equal layer sizes (random weights)
+# --compare nevurax / redirax / lenuzen: that design beside Qwen2 at equal layer sizes (random weights)
 # ---------------------------------------------------------------------------------------------------------
 def _nevurax_shape(width, heads, kv_heads, head, inter, vocab, layers, window, experts, top):
     """A Nevurax model whose layers are as large as a Qwen2 layer of the given sizes: the mixers have as many
@@ -495,7 +495,21 @@ def _redirax_shape(width, heads, kv_heads, head, inter, vocab, layers, window, e
                        for i in range(layers)]}
 
 
-COMPARE_DESIGNS = {"nevurax": _nevurax_shape, "redirax": _redirax_shape}
+def _lenuzen_shape(width, heads, kv_heads, head, inter, vocab, layers, window, experts, top):
+    """A Lenuzen model whose layers are as large as a Qwen2 layer of the given sizes: the same heads (values as
+    wide as keys), alternately the windowed attention with a temperature and a gate a head and the chunked one
+    with mixed heads and a sink (window and chunk of ``window`` positions); the feed-forward without a gate has
+    as many weights as the gated one (two matrices of 1.5 x inter hidden units instead of three of inter)."""
+    rot = {"base": 1e6, "dims": head, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
+    mixer = {"heads": heads, "kv_heads": kv_heads, "dim": head, "vdim": head, "scale": 8.0 * head ** -0.5,
+             "mask": {"size": window}, "rot": rot}
+    return {"architecture": "Lenuzen", "vocab": vocab, "width": width, "embedding": {"scale": width ** 0.5},
+            "norm": {"eps": 1e-6}, "logit_scale": 1.0,
+            "layers": [{"type": "attention" if i % 2 == 0 else "attention_2", "mixer": mixer,
+                        "mlp": {"kind": "dense", "ff": 3 * inter // 2 // 64 * 64}} for i in range(layers)]}
+
+
+COMPARE_DESIGNS = {"nevurax": _nevurax_shape, "redirax": _redirax_shape, "lenuzen": _lenuzen_shape}
 
 COMPARE_SIZES = {
     # name: (Qwen2 sizes, window of the latent attention, experts, top)
@@ -585,8 +599,11 @@ def run_compare(args):
             row[design] = r
             del engine
             torch.cuda.empty_cache()
-        row["config"] = {design_name: {"window": window if design_name == "nevurax" else None, "experts": experts,
-                                       "top": top, "expert_ff": nev["layers"][-1]["mlp"]["expert"]["ff"]}}
+        if design_name == "lenuzen":
+            row["config"] = {design_name: {"window": window, "chunk": window, "ff": nev["layers"][-1]["mlp"]["ff"]}}
+        else:
+            row["config"] = {design_name: {"window": window if design_name == "nevurax" else None, "experts": experts,
+                                           "top": top, "expert_ff": nev["layers"][-1]["mlp"]["expert"]["ff"]}}
         out["sizes"][name] = row
     print(json.dumps(out))
     return 0
@@ -696,7 +713,7 @@ def main():
                     help="with --only: the layer sizes of that workload's model instead of Qwen2-1.5B's")
     ap.add_argument("--design-only", action="store_true", dest="design_only",
                     help="with --compare: leave the Qwen2 arm out")
-    ap.add_argument("--compare", default="", choices=["", "nevurax", "redirax"],
+    ap.add_argument("--compare", default="", choices=["", "nevurax", "redirax", "lenuzen"],
                     help="instead of the headline measurement: prefill and decode of a few layers of that design beside "
                          "Qwen2 at equal layer sizes (random weights); --layers (default 4), --size, --kernels go with it")
     ap.add_argument("--size", default="", dest="shape_name", choices=[""] + sorted(COMPARE_SIZES),

@@ -49,6 +49,7 @@ LIBRARIES: Dict[str, Tuple[Tuple[str, ...], Tuple[str, ...]]] = {
     "streams": (("streams.cu",), ()),
     "linear_attn": (("linear_attention.cu",), ()),
     "attn_mod": (("qkv_norm_rotate_store.cu", "attention_modulated.cu"), ()),
+    "attn_shaped": (("attention_shaped_mma.cu",), ()),
 }
 
 _INCLUDE = re.compile(r'^\s*#\s*include\s+"([^"]+)"', re.M)

@@ -16,6 +16,11 @@
 // q is written back in place, rounded once; k and v go to the token's cache slot, so the cache holds them
 // normalised.  One block a token, the row in shared memory.
 //
+// With `mix` (float32 [nh, nh]) the kernel also leaves, for an attention that mixes its heads' scores by that
+// matrix, the queries such an attention can take in one product: s'_h = sum_a mix[h, a] t_a (q_a . k_kv(a)) is
+// Q'_h . [k_0 | .. | k_(nkv-1)] with Q'_h[c * hd + d] = sum over the heads a of kv head c of mix[h, a] t_a q_a[d]
+// (t: `mix_temp`, float32 [nh], optional).  qmix [tokens, nh, nkv * hd], made from the float32 row, rounded once.
+//
 // Cache plane: K [num_pages, nkv, page_size, hd], V [num_pages, nkv, page_size, vd].
 #include "common.cuh"
 
@@ -26,7 +31,8 @@ qkv_norm_rotate_store_kernel(T* __restrict__ qkv, long qkv_stride, const float* 
                              int interleaved, int nh, int nkv, int hd, int vd, int norm_mode,
                              const float* __restrict__ qw, const float* __restrict__ kw, int value_norm, float eps,
                              const int* __restrict__ slot_map, T* __restrict__ k_cache, T* __restrict__ v_cache,
-                             int page_size, long num_slots, int* status) {
+                             int page_size, long num_slots, const float* __restrict__ mix,
+                             const float* __restrict__ mix_temp, T* __restrict__ qmix, int* status) {
   extern __shared__ float row[];          // [(nh + nkv) * hd + nkv * vd], then cos and sin [rot_dim / 2] each
   __shared__ float scratch[32];
   LL_PDL_TRIGGER();
@@ -86,6 +92,18 @@ qkv_norm_rotate_store_kernel(T* __restrict__ qkv, long qkv_stride, const float* 
   const long page = slot >= 0 ? slot / page_size : 0;
   const int off = slot >= 0 ? (int)(slot - page * page_size) : 0;
   for (int i = tid; i < qn; i += blockDim.x) g[i] = from_f32<T>(row[i]);
+  if (mix != nullptr && qmix != nullptr) {
+    const int group = nh / nkv, wide = nkv * hd;
+    T* dst = qmix + (size_t)t * nh * wide;
+    for (int i = tid; i < nh * wide; i += blockDim.x) {
+      const int h = i / wide, rem = i - h * wide;
+      const int kl = rem / hd, d = rem - kl * hd;
+      float s = 0.f;
+      for (int a = kl * group; a < (kl + 1) * group; ++a)
+        s = fmaf(mix[h * nh + a] * (mix_temp ? mix_temp[a] : 1.0f), row[(size_t)a * hd + d], s);
+      dst[i] = from_f32<T>(s);
+    }
+  }
   if (slot >= 0) {
     for (int i = tid; i < kn; i += blockDim.x) {
       const int h = i / hd, j = i - h * hd;
@@ -102,7 +120,8 @@ extern "C" int ll_qkv_norm_rotate_store(int dtype, void* qkv, long qkv_stride, c
                                         const float* freq, int rot_dim, float amp, int interleaved, int nh, int nkv,
                                         int hd, int vd, int norm_mode, const float* qw, const float* kw, int value_norm,
                                         float eps, const int* slot_map, void* k_cache, void* v_cache, int page_size,
-                                        long num_slots, int num_tokens, int* status, cudaStream_t stream) {
+                                        long num_slots, int num_tokens, const float* mix, const float* mix_temp,
+                                        void* qmix, int* status, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   if (rot_dim < 0 || rot_dim > hd || (rot_dim & 1) || hd <= 0 || vd <= 0 || norm_mode < 0 || norm_mode > 2 ||
       (norm_mode == 2 && (qw == nullptr || kw == nullptr)) || (rot_dim > 0 && freq == nullptr))
@@ -114,7 +133,7 @@ extern "C" int ll_qkv_norm_rotate_store(int dtype, void* qkv, long qkv_stride, c
       cudaFuncSetAttribute(qkv_norm_rotate_store_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     ll_launch(qkv_norm_rotate_store_kernel<T>, dim3(num_tokens), dim3(256), smem, stream, (T*)qkv, qkv_stride, bias,
               positions, freq, rot_dim, amp, interleaved, nh, nkv, hd, vd, norm_mode, qw, kw, value_norm, eps, slot_map,
-              (T*)k_cache, (T*)v_cache, page_size, num_slots, status);
+              (T*)k_cache, (T*)v_cache, page_size, num_slots, mix, mix_temp, (T*)qmix, status);
   });
   return LL_LAUNCH_RESULT();
 }

@@ -1564,12 +1564,24 @@ def qkv_norm_rotate_store(qkv: torch.Tensor, bias: Optional[torch.Tensor], posit
                           num_kv_heads: int, head_dim: int, value_head_dim: int, qk_norm: Optional[str],
                           q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], value_norm: bool,
                           eps: float, slot_map: Optional[torch.Tensor], k_cache: Optional[torch.Tensor],
-                          v_cache: Optional[torch.Tensor], page_size: int, status: Optional[torch.Tensor]) -> None:
+                          v_cache: Optional[torch.Tensor], page_size: int, status: Optional[torch.Tensor],
+                          head_mix: Optional[torch.Tensor] = None, mix_temperature: Optional[torch.Tensor] = None,
+                          mixed_q: Optional[torch.Tensor] = None) -> None:
     """Bias, the norms of q, k and v (``qk_norm``: "projection": an RMS norm with weights over all of q and all of
     k before the rotation; "head_unit": every head divided by its root mean square after it; ``value_norm``: the
     same for every value head), the rotation by angles made in the kernel (cos and sin times ``amplitude``), and
-    the store of k and v.  In place on the first (nh + nkv) * head_dim + nkv * value_head_dim columns of ``qkv``."""
-    _need_cuda(qkv, bias, positions, freq, q_weight, k_weight, slot_map, k_cache, v_cache)
+    the store of k and v.  In place on the first (nh + nkv) * head_dim + nkv * value_head_dim columns of ``qkv``.
+    With ``head_mix`` [nh, nh] and ``mixed_q`` [tokens, nh * nkv * head_dim] also the queries of an attention that
+    mixes its heads' scores, as one wider query a head over all kv heads' keys side by side (``attn_shaped``)."""
+    _need_cuda(qkv, bias, positions, freq, q_weight, k_weight, slot_map, k_cache, v_cache, head_mix, mix_temperature,
+               mixed_q)
+    _f32(head_mix, "head_mix")
+    _f32(mix_temperature, "mix_temperature")
+    if mixed_q is not None:
+        _need(head_mix is not None and tuple(head_mix.shape) == (num_heads, num_heads) and head_mix.is_contiguous(),
+              "mixed queries need head_mix [heads, heads]")
+        _need(mixed_q.dtype == qkv.dtype and mixed_q.is_contiguous()
+              and tuple(mixed_q.shape) == (qkv.shape[0], num_heads * num_kv_heads * head_dim), "mixed_q shape")
     for t, nm in ((bias, "bias"), (freq, "freq"), (q_weight, "q norm weight"), (k_weight, "k norm weight")):
         _f32(t, nm)
     _i32(positions, "positions")
@@ -1596,7 +1608,67 @@ def qkv_norm_rotate_store(qkv: torch.Tensor, bias: Optional[torch.Tensor], posit
         _ptr(positions), _ptr(freq), c_int(rot_dim), c_float(amplitude), c_int(1 if interleaved else 0),
         c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(value_head_dim), c_int(mode), _ptr(q_weight),
         _ptr(k_weight), c_int(1 if value_norm else 0), c_float(eps), _ptr(slot_map), _ptr(k_cache), _ptr(v_cache),
-        c_int(page_size), c_long(num_slots), c_int(qkv.shape[0]), _ptr(status), _stream())
+        c_int(page_size), c_long(num_slots), c_int(qkv.shape[0]), _ptr(head_mix if mixed_q is not None else None),
+        _ptr(mix_temperature), _ptr(mixed_q), _ptr(status), _stream())
+
+
+def attn_shaped_supported(dtype: torch.dtype, num_kv_heads: int, head_dim: int, value_head_dim: int, page_size: int,
+                          q_stride: int, mixed: bool) -> bool:
+    """Whether the tensor-core attention with shaped scores takes this shape (else ``attention_modulated``)."""
+    if not (dtype == torch.bfloat16 and head_dim in (64, 128) and value_head_dim in (64, 128)
+            and page_size % 16 == 0 and q_stride % 8 == 0):
+        return False
+    stage = 2 * 64 * (num_kv_heads if mixed else 1) * head_dim * 2 + 2 * 64 * value_head_dim * 2
+    return stage <= 200 * 1024
+
+
+def attn_shaped_blocks(q_lens, group: int) -> int:
+    """Row blocks of these entries for ``attn_shaped``: a CTA takes 128 (token, head of the group) rows of one entry."""
+    return sum((int(n) * group + 127) // 128 for n in q_lens)
+
+
+def attn_shaped(out: torch.Tensor, q: torch.Tensor, q_stride: int, mixed: bool, gate: Optional[torch.Tensor],
+                temperature: Optional[torch.Tensor], k_cache: torch.Tensor, v_cache: torch.Tensor,
+                block_table: torch.Tensor, cu_q: torch.Tensor, ctx_len: torch.Tensor, req_slot: torch.Tensor,
+                num_entries: int, row_blocks: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                value_head_dim: int, page_size: int, mask: str, mask_size: Optional[int], sink: bool, scale: float,
+                status: Optional[torch.Tensor], nsplit: int = 1, span: int = 1) -> None:
+    """Tensor-core paged attention (bfloat16) with shaped scores: the mechanisms of ``attention_modulated`` for
+    head sizes 64 and 128.  ``q``: the projection's rows (head h at h * head_dim), or with ``mixed`` the wider
+    queries that ``qkv_norm_rotate_store`` leaves for mixed heads (then ``temperature`` is inside them).
+    ``nsplit`` > 1 (every entry brings one token): the keys of a row are cut into parts of ``span`` stages of 64
+    keys, each a CTA, joined by a second kernel; nsplit * span must cover the stages any token sees.  Launches one
+    kernel, two with ``nsplit`` > 1."""
+    _need_cuda(out, q, gate, temperature, k_cache, v_cache, block_table, cu_q, ctx_len, req_slot)
+    for t, nm in ((block_table, "block_table"), (cu_q, "cu_q"), (ctx_len, "ctx_len"), (req_slot, "req_slot")):
+        _i32(t, nm)
+    _f32(temperature, "temperature")
+    _need(attn_shaped_supported(q.dtype, num_kv_heads, head_dim, value_head_dim, page_size, q_stride, mixed),
+          "attn_shaped takes bfloat16, head sizes 64 and 128 and pages of a multiple of 16 tokens")
+    _need(out.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and v_cache.dtype == torch.bfloat16,
+          "attn_shaped: dtypes differ")
+    _need(out.stride(1) == 1 and out.shape[1] == num_heads * value_head_dim and out.stride(0) % 8 == 0,
+          "attn_shaped: out")
+    _need(k_cache.is_contiguous() and v_cache.is_contiguous(), "cache plane must be contiguous")
+    _need(tuple(k_cache.shape[1:]) == (num_kv_heads, page_size, head_dim)
+          and tuple(v_cache.shape[1:]) == (num_kv_heads, page_size, value_head_dim), "cache plane shape")
+    _need(cu_q.numel() >= num_entries + 1 and ctx_len.numel() >= num_entries and req_slot.numel() >= num_entries,
+          "attn_shaped: entry arrays too short")
+    _need(temperature is None or temperature.numel() == num_heads, "temperature: a number a head")
+    _need(gate is None or (gate.dtype == q.dtype and gate.stride(1) == 1), "gate: [tokens, heads] rows")
+    _need(mask == "causal" or (mask_size or 0) > 0, "a window or chunks need a size")
+    part = None
+    if nsplit > 1:
+        part = torch.empty((out.shape[0], num_heads, nsplit, value_head_dim + 2), dtype=torch.float32,
+                           device=out.device)
+    load_library("attn_shaped").call(
+        "ll_attn_shaped", _ptr(out), c_long(out.stride(0)), _ptr(q), c_long(q_stride), c_int(1 if mixed else 0),
+        _ptr(gate), c_long(0 if gate is None else gate.stride(0)), _ptr(temperature), _ptr(k_cache), _ptr(v_cache),
+        _ptr(block_table), c_int(block_table.stride(0)), _ptr(cu_q), _ptr(ctx_len), _ptr(req_slot),
+        c_int(num_entries), c_int(row_blocks), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim),
+        c_int(value_head_dim), c_int(page_size), c_int(k_cache.shape[0]), c_int(ATTN_MASK[mask]),
+        c_int(int(mask_size or 0)), c_int(1 if sink else 0), c_float(scale), c_int(nsplit), c_int(span), _ptr(part),
+        _ptr(status), _stream())
 
 
 def attention_modulated(out: torch.Tensor, q: torch.Tensor, q_stride: int, gate: Optional[torch.Tensor],

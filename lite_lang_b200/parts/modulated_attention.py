@@ -22,6 +22,10 @@ One part, every mechanism a parameter, so that a design picks the ones it has:
 The cache holds keys rotated and normalised and values normalised, one plane of pages; with a window or chunks
 the pages that no later token can read go back to the pool while the request lives.  Scores, softmax weights,
 norms and angles are float32 whatever the engine's dtype is.  q | k | v (| gate) are one product.
+
+Kernels: in bfloat16 with head sizes 64 and 128, tensor cores (``attn_shaped``: prompt portions 128 rows a CTA,
+single tokens with their keys split over CTAs; mixed heads as one wider query a head, made where q is
+normalised); every other size, and float32, a block a token in float32 arithmetic (``attention_modulated``).
 """
 
 from __future__ import annotations
@@ -104,6 +108,9 @@ class ModulatedAttention(Mixer):
     def load(self, fetch, dtype, device) -> None:
         nm = self.names
         w = [fetch(nm[r]).to(dtype) for r in (("q", "k", "v", "gate") if self.head_gate else ("q", "k", "v"))]
+        rows = sum(t.shape[0] for t in w)
+        if rows % 8:      # rows of the product start on 16-byte boundaries (the tensor-core attention reads q so)
+            w.append(torch.zeros((8 - rows % 8, self.hidden_size), dtype=dtype, device=w[0].device))
         self.w_in = torch.cat(w, dim=0).to(device).contiguous()
         if self.qkv_bias:
             b = [fetch(nm[r]).to(torch.float32) for r in ("q_bias", "k_bias", "v_bias")]
@@ -133,6 +140,8 @@ class ModulatedAttention(Mixer):
         libs = ["core", "attn_mod"]
         if self.w_in is not None and self.w_in.dtype == torch.bfloat16:
             libs.extend(["gemm_smallm", "gemm_stream", "gemm_tc"])
+            if self.head_dim in (64, 128) and self.vdim in (64, 128):
+                libs.append("attn_shaped")
         return libs
 
     def prepare(self, device, dtype) -> None:
@@ -144,21 +153,66 @@ class ModulatedAttention(Mixer):
         n = x.shape[0]
         proj = ops.linear(x, self.w_in)                  # q | k | v (| gate inputs)
         pos = self.position
+        # bfloat16 with head sizes the tensor-core kernel takes: mixed heads become one wider query a head
+        shaped = ops.attn_shaped_supported(proj.dtype, self.num_kv_heads, self.head_dim, self.vdim, cache.page_size,
+                                           proj.stride(0), self.head_mix)
+        mixed_q = None
+        if shaped and self.head_mix:
+            mixed_q = torch.empty((n, self.num_heads * self.num_kv_heads * self.head_dim), dtype=proj.dtype,
+                                  device=proj.device)
         ops.qkv_norm_rotate_store(
             proj, self.b_in, step.positions, None if pos is None else pos.freq,
             1.0 if pos is None else pos.amplitude, bool(pos is None or pos.interleaved), self.num_heads,
             self.num_kv_heads, self.head_dim, self.vdim, self.qk_norm, self.q_norm_w, self.k_norm_w, self.value_norm,
-            self.eps, cache.slot_map if cache.writable else None, cache.k, cache.v, cache.page_size, step.status)
+            self.eps, cache.slot_map if cache.writable else None, cache.k, cache.v, cache.page_size, step.status,
+            head_mix=self.mix if mixed_q is not None else None,
+            mix_temperature=self.temperature if mixed_q is not None else None, mixed_q=mixed_q)
         attn = torch.empty((n, self.o_width), dtype=x.dtype, device=x.device)
-        self.attend(attn, proj, step, cache)
+        if shaped:
+            self.attend_shaped(attn, proj, mixed_q, step, cache)
+        else:
+            self.attend(attn, proj, step, cache)
         return ops.linear(attn, self.w_o, partial_ok=self.partial_ok)
 
+    def _gate(self, proj):
+        return proj[:, self.gate_offset:self.gate_offset + self.num_heads] if self.head_gate else None
+
     def attend(self, out, proj, step, cache) -> None:
-        gate = proj[:, self.gate_offset:self.gate_offset + self.num_heads] if self.head_gate else None
-        ops.attention_modulated(out, proj, proj.stride(0), gate, cache.k, cache.v, cache.block_table, step.token_req,
-                                step.req_slot, step.positions, proj.shape[0], self.num_heads, self.num_kv_heads,
-                                self.head_dim, self.vdim, cache.page_size, self.mask, self.mask_size, self.sink,
-                                self.scale, self.temperature, self.mix, step.status)
+        """Any sizes, both dtypes, float32 arithmetic: a block a token."""
+        ops.attention_modulated(out, proj, proj.stride(0), self._gate(proj), cache.k, cache.v, cache.block_table,
+                                step.token_req, step.req_slot, step.positions, proj.shape[0], self.num_heads,
+                                self.num_kv_heads, self.head_dim, self.vdim, cache.page_size, self.mask,
+                                self.mask_size, self.sink, self.scale, self.temperature, self.mix, step.status)
+
+    def attend_shaped(self, out, proj, mixed_q, step, cache) -> None:
+        """Tensor cores.  Single-token entries come first in a step: their keys are cut into parts of one or more
+        stages of 64 keys, a CTA each (how many follows from the mask's size, so a position's sums keep their
+        order); the portions of prompts after them share the keys among 128 rows a CTA."""
+        q = proj if mixed_q is None else mixed_q
+        group = self.num_heads // self.num_kv_heads
+        n_single = step.num_single
+        n_rest = step.num_entries - n_single
+        tail = (self.num_heads, self.num_kv_heads, self.head_dim, self.vdim, cache.page_size, self.mask,
+                self.mask_size, self.sink, self.scale, step.status)
+        head = (out, q, q.stride(0), mixed_q is not None, self._gate(proj), self.temperature, cache.k, cache.v,
+                cache.block_table)
+        if n_single > 0:
+            if self.mask == "causal":
+                stages = (int(step.max_kv_len) + 63) // 64 + 1
+            else:
+                stages = (self.mask_size + 62) // 64 + 1
+            span = (stages + 31) // 32
+            nsplit = (stages + span - 1) // span
+            ops.attn_shaped(*head, step.cu_q, step.ctx_len, step.req_slot, n_single, n_single * ((group + 127) // 128),
+                            *tail, nsplit=nsplit, span=span)
+        if n_rest > 0:
+            key = ("attn_shaped", group)
+            blocks = step.scratch.get(key)
+            if blocks is None:
+                blocks = step.scratch[key] = ops.attn_shaped_blocks(
+                    (len(e.tokens) for e in step.entries[n_single:]), group)
+            ops.attn_shaped(*head, step.cu_q[n_single:], step.ctx_len[n_single:], step.req_slot[n_single:], n_rest,
+                            blocks, *tail)
 
 
 register_part("mixer", "modulated_attention", ModulatedAttention)

@@ -94,8 +94,10 @@ def scaled_frequencies(rot: Mapping) -> (torch.Tensor, float):
     return b / factor * g + b * (1.0 - g), 0.1 * math.log(factor) + 1.0
 
 
-def rotate(u: torch.Tensor, pos: torch.Tensor, rot: Mapping) -> torch.Tensor:
+def rotate(u: torch.Tensor, pos: torch.Tensor, rot: Optional[Mapping]) -> torch.Tensor:
     """u [T, heads, d]; pairs (2i, 2i+1) of the first r channels turned, the rest kept."""
+    if not rot:
+        return u
     r = int(rot["dims"])
     if r == 0:
         return u
@@ -135,6 +137,18 @@ def softmax_with_sink(s: torch.Tensor, vis: torch.Tensor) -> torch.Tensor:
     return e / (torch.exp(-m) + e.sum(-1, keepdim=True))
 
 
+def shaped_attention(q, k, v, scale, vis, temp=None, mix=None, sink=False, gate=None):
+    """q [T, H, d], k [T, G, d], v [T, G, dv], vis [T, T] -> [T, H, dv].  temp [H]: a factor a head on the
+    scores; mix [H, H]: the heads' scores of a (query, key) pair mixed; gate [T, H]: a factor on the outputs."""
+    H, G = q.shape[1], k.shape[1]
+    s = torch.stack([(q[:, a] @ k[:, a // (H // G)].T) * scale * (1.0 if temp is None else temp[a]) for a in range(H)])
+    if mix is not None:
+        s = torch.einsum("ab,bij->aij", mix, s)
+    soft = softmax_with_sink if sink else softmax_masked
+    o = torch.stack([soft(s[a], vis) @ v[:, a // (H // G)] for a in range(H)], dim=1)
+    return o if gate is None else o * gate[:, :, None]
+
+
 # --------------------------------------------------------------------------
 # mixers
 # --------------------------------------------------------------------------
@@ -145,18 +159,14 @@ def mixer_a(x: torch.Tensor, pos: torch.Tensor, m: Mapping, w: Mapping[str, torc
     q = (x @ w[p + "q"].T + w[p + "q.b"]).view(T, H, d)
     k = (x @ w[p + "k"].T + w[p + "k.b"]).view(T, G, d)
     v = (x @ w[p + "v"].T + w[p + "v.b"]).view(T, G, dv)
-    q = unit_rms(rotate(q, pos, m["rot"]), eps)
-    k = unit_rms(rotate(k, pos, m["rot"]), eps)
+    q = unit_rms(rotate(q, pos, m.get("rot")), eps)
+    k = unit_rms(rotate(k, pos, m.get("rot")), eps)
     v = unit_rms(v, eps)
     gate = sigmoid(x @ w[p + "g"].T)                  # [T, H]
     size = (m.get("mask") or {}).get("size")
     vis = visible_window(T, int(size) if size else T)
-    heads = []
-    for a in range(H):
-        g = a // (H // G)
-        s = (q[:, a] @ k[:, g].T) * float(m["scale"]) * w[p + "temp"][a]
-        heads.append((softmax_masked(s, vis) @ v[:, g]) * gate[:, a:a + 1])
-    return torch.cat(heads, dim=-1) @ w[p + "o"].T
+    o = shaped_attention(q, k, v, float(m["scale"]), vis, temp=w[p + "temp"], gate=gate)
+    return o.reshape(T, H * dv) @ w[p + "o"].T
 
 
 def mixer_b(x: torch.Tensor, pos: torch.Tensor, m: Mapping, w: Mapping[str, torch.Tensor], p: str, eps: float):
@@ -165,14 +175,12 @@ def mixer_b(x: torch.Tensor, pos: torch.Tensor, m: Mapping, w: Mapping[str, torc
     q = unit_rms(x @ w[p + "q"].T, eps) * w[p + "q.norm"]
     k = unit_rms(x @ w[p + "k"].T, eps) * w[p + "k.norm"]
     v = (x @ w[p + "v"].T).view(T, G, dv)
-    q = rotate(q.view(T, H, d), pos, m["rot"])
-    k = rotate(k.view(T, G, d), pos, m["rot"])
-    s = torch.stack([(q[:, a] @ k[:, a // (H // G)].T) * float(m["scale"]) for a in range(H)])   # [H, T, T]
-    t = torch.einsum("ab,bij->aij", w[p + "talk"], s)
+    q = rotate(q.view(T, H, d), pos, m.get("rot"))
+    k = rotate(k.view(T, G, d), pos, m.get("rot"))
     size = (m.get("mask") or {}).get("size")
     vis = visible_chunk(T, int(size) if size else T)
-    heads = [softmax_with_sink(t[a], vis) @ v[:, a // (H // G)] for a in range(H)]
-    return torch.cat(heads, dim=-1) @ w[p + "o"].T
+    o = shaped_attention(q, k, v, float(m["scale"]), vis, mix=w[p + "talk"], sink=True)
+    return o.reshape(T, H * dv) @ w[p + "o"].T
 
 
 def feed_forward(x: torch.Tensor, w: Mapping[str, torch.Tensor], p: str) -> torch.Tensor:
