@@ -55,6 +55,9 @@ struct AttnTcParams {
   // partial results (unnormalised O, reference maximum, sum) meet in scratch memory, the last CTA to
   // arrive (a counter per row block and kv head, left at zero again) merges them
   int nsplit, row_blocks, split_len;
+  // a gate a head on the output (optional): out[token, head] *= sigmoid(gate[token * gate_stride + head]), float32
+  const bf16* gate;
+  long gate_stride;
   float* scratch;      // [row blocks * nkv * nsplit][HD + 2][128]
   int* counters;       // [row blocks * nkv], zero between launches
   int* status;
@@ -425,6 +428,13 @@ attn_prefill_tc_kernel(const AttnTcParams p, const __grid_constant__ CUtensorMap
     } else {
       inv = l_run > 0.f ? 1.0f / l_run : 0.f;
     }
+    if (finish && p.gate != nullptr) {
+      const int tt = r / p.group, gg = r - tt * p.group;
+      if (r < p.tpb * p.group && tt < ntok) {
+        const float gv = __bfloat162float(p.gate[(size_t)(tok0 + tt) * p.gate_stride + (size_t)(kvh * p.group + gg)]);
+        inv *= 1.0f / (1.0f + expf(-gv));
+      }
+    }
     // ---- normalise; rows leave through shared memory (the Q tile is no longer read) ----
     if (finish) {
       unsigned char* orow = q_s + r * (HD * 2);
@@ -488,12 +498,11 @@ static at_encode_fn at_encoder() {
 // nsplit in 1..8: CTAs a row block's key blocks may be split over, each taking about split_len blocks of 64 keys; with nsplit > 1, scratch is float32
 // [row_blocks * nkv * nsplit * (hd + 2) * 128] and counters int32 [row_blocks * nkv], zero at the first launch
 // (the kernel leaves them zero).
-extern "C" int ll_attn_prefill_tc(void* out, long out_stride, const void* q, long q_stride, int num_tokens,
-                                  const void* k_cache, const void* v_cache, const int* block_table, int bt_stride,
-                                  const int* cu_q, const int* ctx_len, const int* req_slot, int n_entries,
-                                  int row_blocks, int nh, int nkv, int hd, int page_size, int num_pages, int window,
-                                  float scale, int nsplit, int split_len, float* scratch, int* counters,
-                                  int* status, cudaStream_t stream) {
+static int at_run(void* out, long out_stride, const void* q, long q_stride, int num_tokens, const void* k_cache,
+                  const void* v_cache, const int* block_table, int bt_stride, const int* cu_q, const int* ctx_len,
+                  const int* req_slot, int n_entries, int row_blocks, int nh, int nkv, int hd, int page_size,
+                  int num_pages, int window, float scale, int nsplit, int split_len, float* scratch, int* counters,
+                  const void* gate, long gate_stride, int* status, cudaStream_t stream) {
   if (row_blocks <= 0 || n_entries <= 0) return 0;
   if ((hd != 64 && hd != 128) || nkv <= 0 || nh % nkv != 0 || nkv > 65535 || nh / nkv > 128)
     return (int)cudaErrorInvalidValue;
@@ -525,6 +534,8 @@ extern "C" int ll_attn_prefill_tc(void* out, long out_stride, const void* q, lon
   p.nsplit = nsplit;
   p.scratch = scratch;
   p.counters = counters;
+  p.gate = (const bf16*)gate;
+  p.gate_stride = gate_stride;
   p.status = status;
 
   CUtensorMap qmap, kmap, vmap;
@@ -559,4 +570,29 @@ extern "C" int ll_attn_prefill_tc(void* out, long out_stride, const void* q, lon
     ll_launch(attn_prefill_tc_kernel<128>, grid, dim3(AT_THREADS), smem, stream, p, qmap, kmap, vmap);
   }
   return LL_LAUNCH_RESULT();
+}
+
+extern "C" int ll_attn_prefill_tc(void* out, long out_stride, const void* q, long q_stride, int num_tokens,
+                                  const void* k_cache, const void* v_cache, const int* block_table, int bt_stride,
+                                  const int* cu_q, const int* ctx_len, const int* req_slot, int n_entries,
+                                  int row_blocks, int nh, int nkv, int hd, int page_size, int num_pages, int window,
+                                  float scale, int nsplit, int split_len, float* scratch, int* counters,
+                                  int* status, cudaStream_t stream) {
+  return at_run(out, out_stride, q, q_stride, num_tokens, k_cache, v_cache, block_table, bt_stride, cu_q, ctx_len, req_slot,
+                n_entries, row_blocks, nh, nkv, hd, page_size, num_pages, window, scale, nsplit, split_len, scratch,
+                counters, nullptr, 0, status, stream);
+}
+
+// The same with a gate a head on the output: gate is bfloat16, gate[token * gate_stride + head], and every head's
+// output row is multiplied by its sigmoid (float32) before it is rounded.
+extern "C" int ll_attn_prefill_tc_gated(void* out, long out_stride, const void* q, long q_stride, int num_tokens,
+                                        const void* k_cache, const void* v_cache, const int* block_table, int bt_stride,
+                                        const int* cu_q, const int* ctx_len, const int* req_slot, int n_entries,
+                                        int row_blocks, int nh, int nkv, int hd, int page_size, int num_pages,
+                                        int window, float scale, int nsplit, int split_len, float* scratch,
+                                        int* counters, const void* gate, long gate_stride, int* status,
+                                        cudaStream_t stream) {
+  return at_run(out, out_stride, q, q_stride, num_tokens, k_cache, v_cache, block_table, bt_stride, cu_q, ctx_len, req_slot,
+                n_entries, row_blocks, nh, nkv, hd, page_size, num_pages, window, scale, nsplit, split_len, scratch,
+                counters, gate, gate_stride, status, stream);
 }

@@ -173,7 +173,7 @@ struct GpParams {
   int m_tiles;      // tiles of 256 tokens
   int tiles;        // m_tiles x column tiles (plain: 256 features a tile, gated: 128)
   int vec_ok;       // the output takes 16-byte pieces (aligned base and stride, N a multiple of 8)
-  int act;          // gated: 0 silu(gate) * up, 1 relu(gate) * up
+  int act;          // gated: 0 silu(gate) * up, 1 relu(gate) * up; plain: 0 none, 1 gelu (tanh form), 2 ReLU, 3 SiLU
   int* status;
   // q|k|v mode only: what follows the projection (N = (nh + 2 nkv) hd; out is q [M, nh hd])
   const float* bias;      // float32 [N] or null
@@ -515,6 +515,21 @@ gemm_pair_kernel(const GpParams p, const __grid_constant__ CUtensorMap wmap, con
             gp_ld_wait(a);
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(a[i]);
+            if (MODE == GP_MODE_PLAIN && p.act != 0) {
+              // the activation of a feed-forward without a gate, on the product rounded to bfloat16 first (as a
+              // product followed by an activation kernel has it); gelu in its tanh form is z * sigmoid(2 u),
+              // u = sqrt(2/pi) (z + 0.044715 z^3); x * rcp(y) for the division, as in the gated mode
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                const float z = __bfloat162float(__float2bfloat16_rn(v[i]));
+                if (p.act == 2) {
+                  v[i] = fmaxf(z, 0.f);
+                } else {
+                  const float u = p.act == 3 ? z : 1.5957691216057308f * (z + 0.044715f * z * z * z);
+                  v[i] = __fdividef(z, 1.0f + __expf(-u));
+                }
+              }
+            }
           }
           if (row < p.M) gp_store32(p, out_row, nt * COLS + 32 * c, v);
         }
@@ -652,6 +667,32 @@ extern "C" int ll_gemm_pair(void* out, long out_stride, const void* x, long x_st
   p.num_slots = 0;
   return gated ? gp_launch<GP_MODE_GATED>(p, w, x, x_stride, sm_count, stream)
                : gp_launch<GP_MODE_PLAIN>(p, w, x, x_stride, sm_count, stream);
+}
+
+// out = act(x W^T) for a feed-forward without a gate: act 1 gelu (tanh form), 2 ReLU, 3 SiLU (0: none), applied to
+// the product as bfloat16 holds it.  Operands as in ll_gemm_pair.
+extern "C" int ll_gemm_pair_act(void* out, long out_stride, const void* x, long x_stride, const void* w, int M, int N,
+                                int K, int act, int sm_count, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || (K % 8) != 0 || (x_stride % 8) != 0 || sm_count < 2 || act < 0 || act > 3)
+    return (int)cudaErrorInvalidValue;
+  GpParams p;
+  p.out = reinterpret_cast<bf16*>(out);
+  p.out_stride = out_stride;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.status = status;
+  p.act = act;
+  p.vec_ok = ((uintptr_t)out % 16 == 0 && out_stride % 8 == 0 && N % 8 == 0) ? 1 : 0;
+  p.bias = nullptr;
+  p.positions = nullptr;
+  p.cos_sin = nullptr;
+  p.slot_map = nullptr;
+  p.k_cache = p.v_cache = nullptr;
+  p.max_pos = p.nh = p.nkv = p.hd = p.page_size = 0;
+  p.num_slots = 0;
+  return gp_launch<GP_MODE_PLAIN>(p, w, x, x_stride, sm_count, stream);
 }
 
 // The q|k|v projection of an attention layer with what follows it: qkv = x W^T (+ bias), q and k rotated by

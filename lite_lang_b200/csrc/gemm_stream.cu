@@ -135,6 +135,16 @@ template <typename OutT> __device__ __forceinline__ OutT gt_out(float v);
 template <> __device__ __forceinline__ float gt_out<float>(float v) { return v; }
 template <> __device__ __forceinline__ bf16 gt_out<bf16>(float v) { return __float2bfloat16_rn(v); }
 
+// The activation of a feed-forward without a gate on a product's result (float32 arithmetic on the value as
+// bfloat16 holds it).  gelu in its tanh form is z * sigmoid(2 u) with u = sqrt(2/pi) (z + 0.044715 z^3).
+__device__ __forceinline__ float gt_row_act(float acc, int act) {
+  const float z = __bfloat162float(__float2bfloat16_rn(acc));
+  if (act == 2) return fmaxf(z, 0.f);
+  if (act == 3) return z / (1.0f + expf(-z));
+  const float u = 0.7978845608028654f * (z + 0.044715f * z * z * z);
+  return z / (1.0f + expf(-2.0f * u));
+}
+
 struct GtParams {
   const bf16* x;
   void* out;
@@ -144,6 +154,8 @@ struct GtParams {
   int ksplit;   // parts the k range is cut into; > 1: out is float32 [ksplit, M, N] partial sums
   int cpp;      // k chunks (stages) per part
   int act;      // GATED: 0 silu(gate) * up, 1 relu(gate) * up
+  int row_act;  // WIDE to bfloat16 with k whole: 0 none; 1 gelu (tanh form), 2 ReLU, 3 SiLU on the result, which is
+                // rounded to bfloat16 first, as a product followed by an activation kernel would have it
   // QKV_ROPE only: what follows the projection
   const float* bias;       // float32 [(nh + 2 nkv) hd] or null
   const int* positions;    // int32 [M]
@@ -446,6 +458,12 @@ gemm_stream_kernel(const GtParams p, const __grid_constant__ CUtensorMap wmap, c
     OutT* out = reinterpret_cast<OutT*>(p.out) + (size_t)kp * p.M * p.out_stride;  // this part's [M, N] block
     if (MODE == GT_MODE_WIDE) {
       const int fa = u * 64 + 16 * warp + g, fb = fa + 8;
+      if (sizeof(OutT) == 2 && p.row_act != 0) {
+#pragma unroll
+        for (int j = 0; j < MT; ++j)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) acc[j][e] = gt_row_act(acc[j][e], p.row_act);
+      }
 #pragma unroll
       for (int j = 0; j < MT; ++j) {
         const int t0 = 8 * j + 2 * c, t1 = t0 + 1;
@@ -658,8 +676,10 @@ extern "C" int ll_gemm_stream(void* out, long out_stride, int out_f32, const voi
                               int M, int N, int K, int mode, int ksplit, int sm_count, int* status,
                               cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
-  const int act = mode >> 8;      // (bits from 8 on: the gated mode's activation, 0 SiLU, 1 ReLU)
+  const int act = (mode >> 8) & 0xff;        // (bits 8..15: the gated mode's activation, 0 SiLU, 1 ReLU)
+  const int row_act = (mode >> 16) & 0xff;   // (bits 16..23: an activation on the wide mode's result, see GtParams)
   mode &= 0xff;
+  if (row_act != 0 && (mode != GT_MODE_WIDE || out_f32 || ksplit != 1 || row_act > 3)) return (int)cudaErrorInvalidValue;
   if (M > 64 || K <= 0 || (x_stride % 8) != 0 || sm_count <= 0 || ksplit < 1) return (int)cudaErrorInvalidValue;
   // (33 to 64 tokens: units of 16 features to bfloat16 only, in two blocks of tokens)
   if (M > 32 && (mode != GT_MODE_NARROW || out_f32 || ksplit != 1)) return (int)cudaErrorInvalidValue;
@@ -673,6 +693,7 @@ extern "C" int ll_gemm_stream(void* out, long out_stride, int out_f32, const voi
   p.N = N;
   p.K = K;
   p.act = act == 1 ? 1 : 0;
+  p.row_act = row_act;
   p.status = status;
   if (mode == GT_MODE_WIDE) {
     if (K % 128) return (int)cudaErrorInvalidValue;

@@ -499,13 +499,14 @@ def attn_prefill_tc(out: torch.Tensor, q: torch.Tensor, q_stride: int, k_cache: 
                     block_table: torch.Tensor, cu_q: torch.Tensor, ctx_len: torch.Tensor, req_slot: torch.Tensor,
                     num_entries: int, row_blocks: int, num_heads: int, num_kv_heads: int, head_dim: int,
                     page_size: int, window: Optional[int], scale: float, status: Optional[torch.Tensor],
-                    nsplit: Optional[int] = None, split_len: int = 8) -> None:
+                    nsplit: Optional[int] = None, split_len: int = 8, gate: Optional[torch.Tensor] = None) -> None:
     """Paged attention for portions of prompts on the tcgen05 tensor cores (TMA loads, S and O in tensor
     memory).  ``row_blocks`` from ``attn_prefill_tc_blocks``.  Otherwise as ``attn_prefill``.
     ``nsplit`` (1, 2, 4, 8; default: by the size of the step): the keys of a row block are split over up to that
     many CTAs of about ``split_len`` blocks of 64 keys each (``attn_prefill_tc_plan`` chooses both), which merge
-    through scratch memory kept by this module (grown when needed, never shrunk)."""
-    _need_cuda(out, q, k_cache, v_cache, block_table, cu_q, ctx_len, req_slot)
+    through scratch memory kept by this module (grown when needed, never shrunk).
+    ``gate`` (bfloat16 [tokens, num_heads], any row stride): every head's output times the sigmoid of its gate."""
+    _need_cuda(out, q, k_cache, v_cache, block_table, cu_q, ctx_len, req_slot, gate)
     for t, nm in ((block_table, "block_table"), (cu_q, "cu_q"), (ctx_len, "ctx_len"), (req_slot, "req_slot")):
         _i32(t, nm)
     _need(attn_prefill_tc_supported(q.dtype, head_dim, page_size, q_stride, num_heads // num_kv_heads),
@@ -532,12 +533,18 @@ def attn_prefill_tc(out: torch.Tensor, q: torch.Tensor, q_stride: int, k_cache: 
                     torch.zeros(max(row_blocks * num_kv_heads, 1024), dtype=torch.int32, device=q.device))
             _attn_tc_scratch[q.device] = have
         scratch, counters = have
-    load_library("attn_tc").call(
-        "ll_attn_prefill_tc", _ptr(out), c_long(out.stride(0)), _ptr(q), c_long(q_stride), c_int(q.shape[0]),
-        _ptr(k_cache), _ptr(v_cache), _ptr(block_table), c_int(block_table.stride(0)), _ptr(cu_q), _ptr(ctx_len),
-        _ptr(req_slot), c_int(num_entries), c_int(row_blocks), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim),
-        c_int(page_size), c_int(k_cache.shape[0]), c_int(window or 0), c_float(scale), c_int(nsplit), c_int(max(1, int(split_len))),
-        _ptr(scratch), _ptr(counters), _ptr(status), _stream())
+    args = (_ptr(out), c_long(out.stride(0)), _ptr(q), c_long(q_stride), c_int(q.shape[0]),
+            _ptr(k_cache), _ptr(v_cache), _ptr(block_table), c_int(block_table.stride(0)), _ptr(cu_q), _ptr(ctx_len),
+            _ptr(req_slot), c_int(num_entries), c_int(row_blocks), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim),
+            c_int(page_size), c_int(k_cache.shape[0]), c_int(window or 0), c_float(scale), c_int(nsplit),
+            c_int(max(1, int(split_len))), _ptr(scratch), _ptr(counters))
+    if gate is not None:
+        _need(gate.dtype == torch.bfloat16 and gate.dim() == 2 and gate.shape[0] == q.shape[0]
+              and gate.shape[1] == num_heads and gate.stride(1) == 1, "attn_prefill_tc: gate is bfloat16 [tokens, heads]")
+        load_library("attn_tc").call("ll_attn_prefill_tc_gated", *args, _ptr(gate), c_long(gate.stride(0)), _ptr(status),
+                                     _stream())
+        return
+    load_library("attn_tc").call("ll_attn_prefill_tc", *args, _ptr(status), _stream())
 
 
 _sample_scratch = {}
@@ -669,17 +676,23 @@ def stream_ksplit(n: int, k: int, mode: int, device) -> int:
 
 
 def gemm_stream(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, mode: int,
-                status: Optional[torch.Tensor] = None, act: str = "silu") -> torch.Tensor:
+                status: Optional[torch.Tensor] = None, act: str = "silu", row_act: Optional[str] = None) -> torch.Tensor:
     """out = x @ weight.T for up to 32 bfloat16 tokens (64 for mode 2 to bfloat16 with k whole) with the TMA
     weight-streaming kernel.
 
     mode 0: units of 64 output features; 1: SiLU-gated (weight [2 I, K], out [M, I]);
     2: units of 16 features with k split over the warps.  A float32 ``out`` of shape
     [parts, M, N] receives partial sums of a k range cut into ``parts`` (see ``stream_ksplit``).
+    ``row_act`` (mode 0 to bfloat16, k whole): an activation of ``ROW_ACT`` on the result.
     """
     _need_cuda(x, weight, out, status)
     m, k = x.shape
     gated = mode == 1
+    row_code = 0
+    if row_act is not None:
+        _need(mode == 0 and out.dim() == 2 and out.dtype == torch.bfloat16, "gemm_stream: an activation goes with mode 0 "
+                                                                          "to bfloat16 and an unsplit k")
+        row_code = ROW_ACT[row_act] + 1
     n = weight.shape[0] // 2 if gated else weight.shape[0]
     _need(stream_mode(x, weight, gated) is not None, "gemm_stream: bfloat16, at most 32 tokens (64 for mode 2), K % 128 == 0")
     _need(mode in (0, 1, 2) and k % (256 if mode == 2 else 128) == 0, "gemm_stream: K does not fit the mode")
@@ -696,7 +709,7 @@ def gemm_stream(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, mode: 
     _need(out.dtype == torch.bfloat16 or (out.dtype == torch.float32 and not gated), "gemm_stream: out dtype")
     load_library("gemm_stream").call(
         "ll_gemm_stream", _ptr(out), c_long(out_stride), c_int(1 if out.dtype == torch.float32 else 0), _ptr(x),
-        c_long(x.stride(0)), _ptr(weight), c_int(m), c_int(n), c_int(k), c_int(mode | (GATE_ACT[act] << 8)),
+        c_long(x.stride(0)), _ptr(weight), c_int(m), c_int(n), c_int(k), c_int(mode | (GATE_ACT[act] << 8) | (row_code << 16)),
         c_int(ksplit), c_int(sm_count(x.device)), _ptr(status if status is not None else TIMELINE_STATUS), _stream())
     return out
 
@@ -896,7 +909,7 @@ def pair_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
 
 
 def gemm_pair(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gated: bool = False,
-              status: Optional[torch.Tensor] = None, act: str = "silu") -> torch.Tensor:
+              status: Optional[torch.Tensor] = None, act: str = "silu", row_act: Optional[str] = None) -> torch.Tensor:
     """out = x @ weight.T for many bfloat16 tokens on the tcgen05 tensor cores, a pair of SMs a tile of
     256 tokens x 256 columns.  ``gated``: weight is [2 I, K] and out = silu(gate) * up, the activation done
     on the accumulator, so gate and up never go to memory."""
@@ -906,6 +919,12 @@ def gemm_pair(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gated: b
     n = weight.shape[0] // 2 if gated else weight.shape[0]
     _need(out.dtype == torch.bfloat16 and out.dim() == 2 and out.shape[0] == m and out.shape[1] == n
           and out.stride(1) == 1, "gemm_pair: out is bfloat16 [M, N] with unit column stride")
+    if row_act is not None:      # a feed-forward without a gate: out = act(x @ weight.T), act of ``ROW_ACT``
+        _need(not gated, "gemm_pair: row_act goes with the plain product")
+        load_library("gemm_pair").call(
+            "ll_gemm_pair_act", _ptr(out), c_long(out.stride(0)), _ptr(x), c_long(x.stride(0)), _ptr(weight), c_int(m),
+            c_int(n), c_int(k), c_int(ROW_ACT[row_act] + 1), c_int(sm_count(x.device)), _ptr(status), _stream())
+        return out
     load_library("gemm_pair").call(
         "ll_gemm_pair", _ptr(out), c_long(out.stride(0)), _ptr(x), c_long(x.stride(0)), _ptr(weight), c_int(m),
         c_int(n), c_int(k), c_int(1 + GATE_ACT[act] if gated else 0), c_int(sm_count(x.device)), _ptr(status),
@@ -1536,6 +1555,23 @@ def round_rows(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
 
 
 ROW_ACT = {"gelu_tanh": 0, "relu": 1, "silu": 2}
+
+
+def linear_act(x: torch.Tensor, weight: torch.Tensor, act: str) -> torch.Tensor:
+    """act(x @ weight.T) for a feed-forward without a gate (``act`` of ``ROW_ACT``).  In bfloat16 the activation is
+    the epilogue of the product where a kernel of this package makes it: the weight-streaming one for a few tokens
+    (units of 64 features, k whole), the two-SM tcgen05 one for many.  Else a product and ``act_rows``."""
+    _need_cuda(x, weight)
+    if (x.dtype == torch.bfloat16 and x.shape[0] <= STREAM_M and stream_mode(x, weight) == 0
+            and not (weight.shape[0] >= 8192 and tc_preferred(x, weight, wide=True))):
+        out = torch.empty((x.shape[0], weight.shape[0]), dtype=x.dtype, device=x.device)
+        return gemm_stream(x, weight, out, 0, row_act=act)
+    if TC_ENABLED and x.shape[0] >= PAIR_MIN_M and pair_supported(x, weight):
+        out = torch.empty((x.shape[0], weight.shape[0]), dtype=x.dtype, device=x.device)
+        return gemm_pair(x, weight, out, row_act=act)
+    out = linear(x, weight)
+    act_rows(out, act)
+    return out
 
 
 def act_rows(x: torch.Tensor, act: str) -> None:

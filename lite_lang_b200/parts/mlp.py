@@ -97,14 +97,13 @@ class DenseMLP(FeedForward):
 
     def kernel_libraries(self):
         bf16 = self.w_down is not None and self.w_down.dtype == torch.bfloat16
-        return ["core", "gemm_smallm", "gemm_stream", "gemm_tc"] if bf16 else ["core"]
+        return ["core", "gemm_smallm", "gemm_stream", "gemm_tc", "gemm_pair"] if bf16 else ["core"]
 
     def weight_bytes(self) -> int:
         return self.w_up.numel() * self.w_up.element_size() + self.w_down.numel() * self.w_down.element_size()
 
     def forward(self, x, step):
-        act = ops.linear(x, self.w_up)
-        ops.act_rows(act, self.activation)
+        act = ops.linear_act(x, self.w_up, self.activation)
         return ops.linear(act, self.w_down, partial_ok=True)
 
 

@@ -25,7 +25,9 @@ norms and angles are float32 whatever the engine's dtype is.  q | k | v (| gate)
 
 Kernels: in bfloat16 with head sizes 64 and 128, tensor cores (``attn_shaped``: prompt portions 128 rows a CTA,
 single tokens with their keys split over CTAs; mixed heads as one wider query a head, made where q is
-normalised); every other size, and float32, a block a token in float32 arithmetic (``attention_modulated``).
+normalised; prompt portions of a design without mixed heads and sink: the plain attention's tcgen05 kernel, the
+temperature on the queries and the gate in its epilogue); every other size, and float32, a block a token in
+float32 arithmetic (``attention_modulated``).
 """
 
 from __future__ import annotations
@@ -142,6 +144,8 @@ class ModulatedAttention(Mixer):
             libs.extend(["gemm_smallm", "gemm_stream", "gemm_tc"])
             if self.head_dim in (64, 128) and self.vdim in (64, 128):
                 libs.append("attn_shaped")
+                if not self.head_mix and not self.sink and self.vdim == self.head_dim:
+                    libs.append("attn_tc")
         return libs
 
     def prepare(self, device, dtype) -> None:
@@ -160,16 +164,18 @@ class ModulatedAttention(Mixer):
         if shaped and self.head_mix:
             mixed_q = torch.empty((n, self.num_heads * self.num_kv_heads * self.head_dim), dtype=proj.dtype,
                                   device=proj.device)
+        # on that path a head's temperature goes onto its query before the query's one rounding
+        fold = shaped and self.head_temperature and not self.head_mix
         ops.qkv_norm_rotate_store(
             proj, self.b_in, step.positions, None if pos is None else pos.freq,
             1.0 if pos is None else pos.amplitude, bool(pos is None or pos.interleaved), self.num_heads,
             self.num_kv_heads, self.head_dim, self.vdim, self.qk_norm, self.q_norm_w, self.k_norm_w, self.value_norm,
             self.eps, cache.slot_map if cache.writable else None, cache.k, cache.v, cache.page_size, step.status,
             head_mix=self.mix if mixed_q is not None else None,
-            mix_temperature=self.temperature if mixed_q is not None else None, mixed_q=mixed_q)
+            mix_temperature=self.temperature if (mixed_q is not None or fold) else None, mixed_q=mixed_q)
         attn = torch.empty((n, self.o_width), dtype=x.dtype, device=x.device)
         if shaped:
-            self.attend_shaped(attn, proj, mixed_q, step, cache)
+            self.attend_shaped(attn, proj, mixed_q, step, cache, None if fold else self.temperature)
         else:
             self.attend(attn, proj, step, cache)
         return ops.linear(attn, self.w_o, partial_ok=self.partial_ok)
@@ -184,17 +190,19 @@ class ModulatedAttention(Mixer):
                                 self.num_kv_heads, self.head_dim, self.vdim, cache.page_size, self.mask,
                                 self.mask_size, self.sink, self.scale, self.temperature, self.mix, step.status)
 
-    def attend_shaped(self, out, proj, mixed_q, step, cache) -> None:
+    def attend_shaped(self, out, proj, mixed_q, step, cache, temperature) -> None:
         """Tensor cores.  Single-token entries come first in a step: their keys are cut into parts of one or more
         stages of 64 keys, a CTA each (how many follows from the mask's size, so a position's sums keep their
-        order); the portions of prompts after them share the keys among 128 rows a CTA."""
+        order); the portions of prompts after them share the keys among 128 rows a CTA.  Portions whose scores are
+        plain by now (no mixed heads, no sink, causal or a window, values as wide as keys; a temperature is on the
+        queries already) go to the tcgen05 kernel of the plain attention, which takes the head gate."""
         q = proj if mixed_q is None else mixed_q
         group = self.num_heads // self.num_kv_heads
         n_single = step.num_single
         n_rest = step.num_entries - n_single
         tail = (self.num_heads, self.num_kv_heads, self.head_dim, self.vdim, cache.page_size, self.mask,
                 self.mask_size, self.sink, self.scale, step.status)
-        head = (out, q, q.stride(0), mixed_q is not None, self._gate(proj), self.temperature, cache.k, cache.v,
+        head = (out, q, q.stride(0), mixed_q is not None, self._gate(proj), temperature, cache.k, cache.v,
                 cache.block_table)
         if n_single > 0:
             if self.mask == "causal":
@@ -205,7 +213,28 @@ class ModulatedAttention(Mixer):
             nsplit = (stages + span - 1) // span
             ops.attn_shaped(*head, step.cu_q, step.ctx_len, step.req_slot, n_single, n_single * ((group + 127) // 128),
                             *tail, nsplit=nsplit, span=span)
-        if n_rest > 0:
+        if (n_rest > 0 and mixed_q is None and temperature is None and not self.sink and self.vdim == self.head_dim
+                and self.mask in ("causal", "window") and ops.TC_ENABLED
+                and ops.attn_prefill_tc_supported(proj.dtype, self.head_dim, cache.page_size, proj.stride(0), group)):
+            window = self.mask_size if self.mask == "window" else None
+            key = ("attn_prefill_tc", group, window)
+            plan = step.scratch.get(key)
+            if plan is None:
+                rest_entries = step.entries[n_single:]
+                ctxs = getattr(step, "entry_ctx", None)
+                if ctxs is not None:
+                    plan = ops.attn_prefill_tc_plan(
+                        [(ctxs[n_single + i], len(e.tokens)) for i, e in enumerate(rest_entries)], group, window,
+                        self.num_kv_heads, 2 * ops.sm_count(proj.device))
+                else:
+                    blocks = ops.attn_prefill_tc_blocks((len(e.tokens) for e in rest_entries), group)
+                    plan = (blocks, ops.attn_prefill_tc_splits(blocks, self.num_kv_heads, proj.device), 8)
+                step.scratch[key] = plan
+            ops.attn_prefill_tc(out, proj, proj.stride(0), cache.k, cache.v, cache.block_table, step.cu_q[n_single:],
+                                step.ctx_len[n_single:], step.req_slot[n_single:], n_rest, plan[0], self.num_heads,
+                                self.num_kv_heads, self.head_dim, cache.page_size, window, self.scale, step.status,
+                                nsplit=plan[1], split_len=plan[2], gate=self._gate(proj))
+        elif n_rest > 0:
             key = ("attn_shaped", group)
             blocks = step.scratch.get(key)
             if blocks is None:

@@ -34,17 +34,17 @@ CASES = {
                        _layer("attention", _mixer(3, 3, 24, 40, 0.33, 7, _rot(10, 10000.0, (4.0, 64, 32.0, 1.0))), 50),
                        _layer("attention_2", _mixer(6, 2, 16, 8, 0.4, 10, _rot(16, 500.0, (3.0, 40, 16.0, 2.0))), 24),
                        _layer("attention", _mixer(1, 1, 36, 20, 0.25, 23, _rot(36, 77.0, (1.5, 30, 8.0, 1.0))), None),
-                       _layer("attention_2", _mixer(1, 1, 20, 44, 0.35, 3, _rot(6, 10000.0, (8.0, 2048, 32.0, 1.0))), 33),
+                       _layer("attention_2", _mixer(1, 1, 20, 44, 0.35, 3, _rot(6, 9000.0, (6.0, 1500, 24.0, 1.0))), 33),
                    ]},
         "seed": 5, "page_size": 4},
     # heads of 64 and 128 with values as wide as keys (the tensor-core kernels in bfloat16), pages of 16, a window
     # and chunks longer than a key tile, a chunk that is no multiple of anything, a logit scale of 1
     "Q": {
         "config": {"architecture": "Lenuzen", "vocab": 300, "width": 128, "embedding": {"scale": 11.3},
-                   "norm": {"eps": 1e-5}, "logit_scale": 1.0,
+                   "norm": {"eps": 2e-5}, "logit_scale": 1.0,
                    "layers": [
                        _layer("attention_2", _mixer(4, 4, 128, 128, 0.13, 48, _rot(128, 10000.0, (2.0, 64, 32.0, 1.0))), 96),
-                       _layer("attention", _mixer(8, 2, 64, 64, 0.19, 40, _rot(32, 1e6, (8.0, 100, 32.0, 1.0))), 64),
+                       _layer("attention", _mixer(8, 2, 64, 64, 0.19, 44, _rot(32, 1e6, (8.0, 100, 32.0, 1.0))), 64),
                        _layer("attention_2", _mixer(8, 2, 64, 64, 0.19, 33, _rot(64, 50000.0, (4.0, 50, 4.0, 0.5))), None),
                        _layer("attention", _mixer(2, 1, 128, 128, 0.13, 77, _rot(64, 10000.0, (16.0, 32, 32.0, 1.0))), 40),
                    ]},

@@ -344,9 +344,11 @@ def _attention_case(dtype, nh, nkv, hd, vd, ps, mask, size, temp, mix, sink, gat
     """Prompt portions and single tokens of several requests in one launch, pages of earlier positions given back.
     The last queries of every request are aimed (a large dot product with one key) at the keys on both sides of
     the edge of what they may read, and at the very first key they may read.  ``kernel``: "blocks" (a block a
-    token, any sizes) or "shaped" (tensor cores; single tokens first, as the batch builder orders a step)."""
+    token, any sizes), "shaped" (tensor cores; single tokens first, as the batch builder orders a step) or "tc" (as
+    "shaped", but the temperature goes onto the queries where the model normalises them and the prompt portions
+    to the plain attention's tcgen05 kernel with the gate in its epilogue)."""
     from lite_lang_b200 import ops
-    if kernel == "shaped":
+    if kernel in ("shaped", "tc"):
         order = sorted(range(len(lens)), key=lambda r: new[r] != 1)
         lens, new = [lens[r] for r in order], [new[r] for r in order]
     rng = np.random.default_rng(hd + seed)
@@ -376,7 +378,7 @@ def _attention_case(dtype, nh, nkv, hd, vd, ps, mask, size, temp, mix, sink, gat
     n_tok = sum(new)
     gate_w = 1 + (torch.randn(n_tok, nh, generator=g) * 2).to(dtype).float() if gate else None
     extra = nh if gate else 0
-    pad = (-(nh * hd + 3 + extra)) % 8 if kernel == "shaped" else 0              # rows on 16-byte boundaries
+    pad = (-(nh * hd + 3 + extra)) % 8 if kernel in ("shaped", "tc") else 0      # rows on 16-byte boundaries
     proj = torch.zeros(n_tok, nh * hd + 3 + extra + pad, dtype=dtype)            # q, three other columns, the gate
     proj[:, :nh * hd] = torch.cat([x.reshape(x.shape[0], -1) for x in qs]).to(dtype)
     if gate:
@@ -402,6 +404,13 @@ def _attention_case(dtype, nh, nkv, hd, vd, ps, mask, size, temp, mix, sink, gat
                                       False, 1e-6, None, None, None, ps, None, head_mix=mvd, mix_temperature=tvd,
                                       mixed_q=q)
             assert torch.equal(rows[:, :nh * hd], proj[:, :nh * hd])
+        if kernel == "tc" and temp:
+            rows = torch.zeros(n_tok, (nh + nkv) * hd + nkv * vd, dtype=dtype, device=dev())
+            rows[:, :nh * hd] = proj[:, :nh * hd]
+            ops.qkv_norm_rotate_store(rows, None, step.positions, None, 1.0, True, nh, nkv, hd, vd, None, None, None,
+                                      False, 1e-6, None, None, None, ps, None, mix_temperature=tvd)
+            proj[:, :nh * hd] = rows[:, :nh * hd]
+            tvd = None
         cu = torch.tensor(np.concatenate([[0], np.cumsum(new)]), dtype=torch.int32, device=dev())
         ctx = torch.tensor([n - c for n, c in zip(lens, new)], dtype=torch.int32, device=dev())
         n_single = sum(1 for c in new if c == 1)
@@ -412,7 +421,14 @@ def _attention_case(dtype, nh, nkv, hd, vd, ps, mask, size, temp, mix, sink, gat
             span = (stages + 31) // 32
             ops.attn_shaped(*head, cu, ctx, step.req_slot, n_single, n_single * ((group + 127) // 128), *tail,
                             nsplit=(stages + span - 1) // span, span=span)
-        if R > n_single:
+        if R > n_single and kernel == "tc":
+            entries = [(lens[r] - new[r], new[r]) for r in range(n_single, R)]
+            blocks, nsplit, split_len = ops.attn_prefill_tc_plan(entries, group, size if mask == "window" else None, nkv,
+                                                                 2 * ops.sm_count(dev()))
+            ops.attn_prefill_tc(out, q, q.stride(0), kc, vc, bt, cu[n_single:], ctx[n_single:], step.req_slot[n_single:],
+                                R - n_single, blocks, nh, nkv, hd, ps, size if mask == "window" else None, scale,
+                                step.status, nsplit=nsplit, split_len=split_len, gate=gate_view)
+        elif R > n_single:
             ops.attn_shaped(*head, cu[n_single:], ctx[n_single:], step.req_slot[n_single:], R - n_single,
                             ops.attn_shaped_blocks(new[n_single:], group), *tail)
     assert int(step.status.item()) == 0
@@ -431,7 +447,7 @@ def _attention_case(dtype, nh, nkv, hd, vd, ps, mask, size, temp, mix, sink, gat
     got = out.float().cpu()
     # (the wider queries of mixed heads are sums of queries rounded once more to bfloat16: with sixteen heads aimed
     # at one key that rounding shows in the scores of the other keys)
-    tol = kernel_tol(dtype) * (2 if kernel == "shaped" and mix else 1)
+    tol = kernel_tol(dtype) * (2 if kernel in ("shaped", "tc") and (mix or (kernel == "tc" and temp)) else 1)
     assert rel_err(got.numpy(), want.numpy()) <= tol, (mask, size)
     return got, want, aimed, vs, new
 
@@ -490,6 +506,41 @@ def test_shaped_scores_on_tensor_cores(nh, nkv, hd, vd, ps):
                     kernel="shaped")
     _attention_case(dt, nh, nkv, hd, vd, ps, "window", 48, False, False, False, False, [5, 70, 9], [1, 1, 1],
                     kernel="shaped")
+
+
+@gpu
+@pytest.mark.parametrize("nh,nkv,hd,ps", [(8, 2, 64, 16), (4, 4, 128, 16), (2, 1, 128, 64), (16, 8, 64, 32), (7, 1, 128, 16)])
+def test_plain_scores_with_temperature_and_gate_on_the_tcgen05_kernel(nh, nkv, hd, ps):
+    """Without mixed heads and sink the prompt portions run on the plain attention's tcgen05 kernel: the
+    temperature on the queries, the gate in the epilogue, windows below, at and above a block of 64 keys, row
+    blocks whose keys are split over CTAs."""
+    dt = torch.bfloat16
+    for size in (7, 64, 65, 33, 1, 129, 1000):
+        _attention_case(dt, nh, nkv, hd, hd, ps, "window", size, True, False, False, True,
+                        [300, 47, 130, 3, 260], [150, 1, 1, 3, 1], seed=size, kernel="tc")
+    _attention_case(dt, nh, nkv, hd, hd, ps, "causal", None, True, False, False, True, [2300, 2200], [200, 1], kernel="tc")
+    _attention_case(dt, nh, nkv, hd, hd, ps, "causal", None, False, False, False, True, [700, 65], [700, 2], kernel="tc")
+    _attention_case(dt, nh, nkv, hd, hd, ps, "window", 200, True, False, False, False, [900], [900], kernel="tc")
+
+
+@gpu
+@pytest.mark.parametrize("M,K,N", [(5, 128, 200), (32, 384, 72), (9, 256, 8192), (200, 96, 136), (300, 200, 333),
+                                   (66, 1536, 520), (3, 90, 33)])
+def test_activation_in_the_epilogue_of_the_product(M, K, N):
+    """act(x W^T) of a feed-forward without a gate: a few tokens through the weight-streaming product, many
+    through the two-SM tcgen05 one, both with the activation on the accumulator; other shapes product, then
+    kernel.  All against the plain gelu of the product rounded to bfloat16."""
+    from lite_lang_b200 import ops
+    g = torch.Generator().manual_seed(M + N)
+    x = (torch.randn(M, K, generator=g)).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * (2.0 / math.sqrt(K))).to(torch.bfloat16)
+    got = ops.linear_act(x.to(dev()), w.to(dev()), "gelu_tanh")
+    z = (x.double() @ w.double().t()).to(torch.bfloat16).double()
+    assert tuple(got.shape) == (M, N) and got.dtype == torch.bfloat16
+    assert rel_err(got.float().cpu().numpy(), P.gelu_tanh(z).numpy()) <= kernel_tol(torch.bfloat16)
+    for act, f in (("relu", lambda t: t.clamp(min=0)), ("silu", lambda t: t * torch.sigmoid(t))):
+        got = ops.linear_act(x.to(dev()), w.to(dev()), act)
+        assert rel_err(got.float().cpu().numpy(), f(z).numpy()) <= kernel_tol(torch.bfloat16)
 
 
 @gpu
