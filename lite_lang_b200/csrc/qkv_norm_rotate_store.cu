@@ -33,13 +33,6 @@
 // Cache plane: K [num_pages, nkv, page_size, hd], V [num_pages, nkv, page_size, vd].
 #include "common.cuh"
 
-template <typename T> __device__ __forceinline__ void qn_store2(T* p, float a, float b);
-template <> __device__ __forceinline__ void qn_store2<float>(float* p, float a, float b) {
-  *reinterpret_cast<float2*>(p) = make_float2(a, b);
-}
-template <> __device__ __forceinline__ void qn_store2<bf16>(bf16* p, float a, float b) {
-  *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
-}
 // eight neighbouring values (p on a 16-byte boundary for bfloat16, a 32-byte one for float32)
 template <typename T> __device__ __forceinline__ void qn_load8(const T* p, float v[8]);
 template <> __device__ __forceinline__ void qn_load8<float>(const float* p, float v[8]) {
@@ -68,8 +61,6 @@ template <> __device__ __forceinline__ void qn_store8<bf16>(bf16* p, const float
   *reinterpret_cast<uint4*>(p) = u;
 }
 
-#define QN_PAIRS 4   // pairs a lane in the mixed queries' loop: head sizes up to 256
-
 // L lanes a head (8, 16 or 32: head sizes up to 8 L), 32 / L heads a warp at a time.
 template <typename T, int L>
 __global__ void __launch_bounds__(256)
@@ -80,7 +71,8 @@ qkv_norm_rotate_store_teams_kernel(T* __restrict__ qkv, long qkv_stride, const f
                                    const int* __restrict__ slot_map, T* __restrict__ k_cache, T* __restrict__ v_cache,
                                    int page_size, long num_slots, const float* __restrict__ mix,
                                    const float* __restrict__ mix_temp, T* __restrict__ qmix, int* status) {
-  extern __shared__ float row[];          // with mix: q as float32 [nh * hd]; then cos and sin [rot_dim / 2] each
+  extern __shared__ __align__(16) float team_row[];   // with mix: q as float32 [nh * hd]; then cos and sin [rot_dim / 2] each
+  float* row = team_row;
   __shared__ float scratch[32];
   LL_PDL_TRIGGER();
   LL_PDL_WAIT();
@@ -186,25 +178,23 @@ qkv_norm_rotate_store_teams_kernel(T* __restrict__ qkv, long qkv_stride, const f
     __syncthreads();
     const int group = nh / nkv, wide = nkv * hd;
     T* dst = qmix + (size_t)t * nh * wide;
-    for (int idx = warp; idx < nh * nkv; idx += nwarps) {      // a warp a (head, kv head): hd values of the wide query
+    for (int i0 = warp * PER; i0 < nh * nkv; i0 += nwarps * PER) {   // a team a (head, kv head): hd values of the wide query
+      const int idx = i0 + team;
+      if (idx >= nh * nkv || e >= hd) continue;
       const int h = idx / nkv, c = idx - h * nkv;
-      float2 acc[QN_PAIRS];
+      float acc[8];
 #pragma unroll
-      for (int j = 0; j < QN_PAIRS; ++j) acc[j] = make_float2(0.f, 0.f);
+      for (int k = 0; k < 8; ++k) acc[k] = 0.f;
       for (int a = c * group; a < (c + 1) * group; ++a) {
         const float coef = mix[h * nh + a] * (mix_temp ? mix_temp[a] : 1.0f);
-        const float* src = row + (size_t)a * hd;
-#pragma unroll
-        for (int j = 0; j < QN_PAIRS; ++j) {
-          const int x = 2 * (lane + 32 * j);
-          if (x < hd) acc[j].x = fmaf(coef, src[x], acc[j].x), acc[j].y = fmaf(coef, src[x + 1], acc[j].y);
-        }
+        const float4 s0 = *reinterpret_cast<const float4*>(row + (size_t)a * hd + e);
+        const float4 s1 = *reinterpret_cast<const float4*>(row + (size_t)a * hd + e + 4);
+        acc[0] = fmaf(coef, s0.x, acc[0]), acc[1] = fmaf(coef, s0.y, acc[1]);
+        acc[2] = fmaf(coef, s0.z, acc[2]), acc[3] = fmaf(coef, s0.w, acc[3]);
+        acc[4] = fmaf(coef, s1.x, acc[4]), acc[5] = fmaf(coef, s1.y, acc[5]);
+        acc[6] = fmaf(coef, s1.z, acc[6]), acc[7] = fmaf(coef, s1.w, acc[7]);
       }
-#pragma unroll
-      for (int j = 0; j < QN_PAIRS; ++j) {
-        const int x = 2 * (lane + 32 * j);
-        if (x < hd) qn_store2<T>(dst + (size_t)h * wide + (size_t)c * hd + x, acc[j].x, acc[j].y);
-      }
+      qn_store8<T>(dst + (size_t)h * wide + (size_t)c * hd + e, acc, 1.0f);
     }
   }
 }
