@@ -8,9 +8,8 @@
 // there.  Entries of one token (decode) have few rows and would leave one CTA to walk all their keys: their
 // launch splits the keys instead, `span` stages a CTA (blockIdx.z), counted from the first stage that the
 // token's mask leaves visible, so that which keys meet in which partial sum depends on the position only.
-// The partial results (unnormalised sums, maximum and sum of a row, float32) meet in global memory; the CTA of a
-// row block that finishes last (a counter a row block and kv head, left at zero again) adds them up in the order
-// of the parts, whoever is last, adds the sink and applies the gate.
+// The partial results (unnormalised sums, maximum and sum of a row, float32) meet in a second small kernel,
+// which also adds the sink and applies the gate.
 //
 // Mixed heads.  s'_h[j] = sum_a M[h, a] (q_a . k_kv(a)[j]) is one dot product of a longer query with the
 // keys of ALL kv heads side by side: with Q'_h = [ sum_{a in group c} M[h, a] q_a  for c = 0 .. nkv-1 ]
@@ -54,7 +53,6 @@ struct AttnShapedParams {
   int* status;
   int nsplit, span;     // nsplit > 1: every entry brings one token; CTA z takes stages [first + z span, + span)
   float* part;          // [tokens, nh, nsplit, VD + 2]: sums, then the maximum (log2 domain) and the sum
-  int* counters;        // nsplit > 1: [row blocks, nkv], zero between launches: the parts of a row block that are done
 };
 
 __device__ __forceinline__ void as_mma(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
@@ -88,35 +86,6 @@ __device__ __forceinline__ int as_first_visible(int mask, int size, int pos) {
   if (mask == 1) return max(0, pos - size + 1);
   if (mask == 2) return (pos / size) * size;
   return 0;
-}
-
-// Rows [r0, r0 + nrows) of kv head kvh of an entry of one token at position pos: out = sum_z part_z 2^(m_z - M) /
-// sum_z l_z 2^(m_z - M) over the parts z in their order, M the largest maximum (0 at least with a sink, whose weight
-// 2^-M joins the denominator), times the head's gate.  How many parts a row has follows from its position as in the
-// kernel that wrote them.  Read past L1: other CTAs wrote the parts.
-template <int VD>
-__device__ __forceinline__ void as_join_rows(const AttnShapedParams& p, int tok, int pos, int kvh, int r0, int nrows,
-                                             int tid) {
-  const int stages = pos / AS_TK - as_first_visible(p.mask, p.mask_size, pos) / AS_TK + 1;
-  const int parts = min(p.nsplit, (stages + p.span - 1) / p.span);
-  for (int idx = tid; idx < nrows * VD; idx += AS_THREADS) {
-    const int r = r0 + idx / VD, d = idx % VD;
-    const int head = kvh * p.group + r;
-    const float* src = p.part + ((size_t)tok * p.nh + head) * p.nsplit * (VD + 2);
-    float M = p.sink ? 0.f : -INFINITY;
-    for (int zz = 0; zz < parts; ++zz) M = fmaxf(M, __ldcg(src + (size_t)zz * (VD + 2) + VD));
-    float L = (p.sink && M > -INFINITY) ? as_exp2(-M) : 0.f, acc = 0.f;
-    for (int zz = 0; zz < parts; ++zz) {
-      const float* sz = src + (size_t)zz * (VD + 2);
-      const float m = __ldcg(sz + VD);
-      const float w = m > -INFINITY ? as_exp2(m - M) : 0.f;
-      L = fmaf(__ldcg(sz + VD + 1), w, L);
-      acc = fmaf(__ldcg(sz + d), w, acc);
-    }
-    float res = L > 0.f ? acc / L : 0.f;
-    if (p.gate) res *= 1.0f / (1.0f + expf(-__bfloat162float(p.gate[(size_t)tok * p.gate_stride + head])));
-    p.out[(size_t)tok * p.out_stride + (size_t)head * VD + d] = __float2bfloat16_rn(res);
-  }
 }
 
 template <int HD, int VD, bool MIX>
@@ -166,8 +135,8 @@ __global__ void __launch_bounds__(AS_THREADS) attn_shaped_kernel(const AttnShape
     tokr[i] = rr / p.group;
     headr[i] = kvh * p.group + (rr - tokr[i] * p.group);
   }
-  if (slot < 0) {  // padding entry: zeros, nothing read (with splits part 0 writes them)
-    if (!split || z == 0) {
+  if (slot < 0) {  // padding entry: zeros, nothing read (with splits the second kernel writes them)
+    if (!split) {
 #pragma unroll
       for (int i = 0; i < 2; ++i)
         if (validr[i]) {
@@ -213,7 +182,7 @@ __global__ void __launch_bounds__(AS_THREADS) attn_shaped_kernel(const AttnShape
   int T_first = cta_lo / AS_TK, T_last = cta_hi / AS_TK;
   if (split) {
     T_first += z * p.span;
-    if (T_first > T_last) return;      // (the join counts the parts of a row from its position)
+    if (T_first > T_last) return;      // the second kernel counts the parts of a row from its position
     if (z < p.nsplit - 1) T_last = min(T_last, T_first + p.span - 1);   // (the last part takes what is left)
   }
 
@@ -436,22 +405,6 @@ __global__ void __launch_bounds__(AS_THREADS) attn_shaped_kernel(const AttnShape
           }
         }
     }
-    // ---- the last part of this row block to get here joins them all ----
-    __shared__ int is_last;
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-      const int stages_all = cta_hi / AS_TK - cta_lo / AS_TK + 1;
-      const int parts_all = min(p.nsplit, (stages_all + p.span - 1) / p.span);
-      int* cnt = p.counters + (size_t)rb * p.nkv + kvh;
-      const int before = atomicAdd(cnt, 1);
-      is_last = before == parts_all - 1;
-      if (is_last) *cnt = 0;           // ready for the next launch
-    }
-    __syncthreads();
-    if (!is_last) return;
-    __threadfence();
-    as_join_rows<VD>(p, tok0, ctx, kvh, r0, min(AS_ROWS, total_rows - r0), tid);
     return;
   }
   // ---- normalise, gate and write: through shared memory, so that rows go out in 16-byte pieces ----
@@ -490,6 +443,39 @@ __global__ void __launch_bounds__(AS_THREADS) attn_shaped_kernel(const AttnShape
   }
 }
 
+// The parts of a single token's rows meet: out[h] = sum_z O_z 2^(m_z - M) / (sum_z l_z 2^(m_z - M) + sink 2^-M),
+// M the largest maximum (0 at least with a sink), times the head's gate.  How many parts a row has follows
+// from its position as in the first kernel.  One block a (entry, head), a thread a value channel.
+template <int VD>
+__global__ void __launch_bounds__(VD) attn_shaped_join_kernel(const AttnShapedParams p) {
+  LL_PDL_WAIT();
+  LL_PDL_TRIGGER();
+  const int e = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
+  const int tok = p.cu_q[e];
+  bf16* o = p.out + (size_t)tok * p.out_stride + (size_t)head * VD;
+  if (p.req_slot[e] < 0) {
+    o[d] = __float2bfloat16_rn(0.f);
+    return;
+  }
+  const int pos = p.ctx_len[e];
+  const int stages = pos / AS_TK - as_first_visible(p.mask, p.mask_size, pos) / AS_TK + 1;
+  const int parts = min(p.nsplit, (stages + p.span - 1) / p.span);
+  const float* src = p.part + ((size_t)tok * p.nh + head) * p.nsplit * (VD + 2);
+  float M = p.sink ? 0.f : -INFINITY;
+  for (int zz = 0; zz < parts; ++zz) M = fmaxf(M, src[(size_t)zz * (VD + 2) + VD]);
+  float L = (p.sink && M > -INFINITY) ? as_exp2(-M) : 0.f, acc = 0.f;
+  for (int zz = 0; zz < parts; ++zz) {
+    const float* s = src + (size_t)zz * (VD + 2);
+    const float m = s[VD];
+    const float w = m > -INFINITY ? as_exp2(m - M) : 0.f;
+    L = fmaf(s[VD + 1], w, L);
+    acc = fmaf(s[d], w, acc);
+  }
+  float r = L > 0.f ? acc / L : 0.f;
+  if (p.gate) r *= 1.0f / (1.0f + expf(-__bfloat162float(p.gate[(size_t)tok * p.gate_stride + head])));
+  o[d] = __float2bfloat16_rn(r);
+}
+
 // Shared memory of a CTA for these sizes (0: the shape is not taken).
 extern "C" long ll_attn_shaped_smem(int nkv, int hd, int vd, int mixed) {
   if ((hd != 64 && hd != 128) || (vd != 64 && vd != 128) || nkv <= 0) return 0;
@@ -509,11 +495,11 @@ extern "C" int ll_attn_shaped(void* out, long out_stride, const void* q, long q_
                               const int* block_table, int bt_stride, const int* cu_q, const int* ctx_len,
                               const int* req_slot, int n_entries, int row_blocks, int nh, int nkv, int hd, int vd,
                               int page_size, int num_pages, int mask, int mask_size, int sink, float scale, int nsplit,
-                              int span, float* part, int* counters, int* status, cudaStream_t stream) {
+                              int span, float* part, int* status, cudaStream_t stream) {
   if (row_blocks <= 0 || n_entries <= 0) return 0;
   const long smem = ll_attn_shaped_smem(nkv, hd, vd, mixed);
   if (smem == 0 || page_size % 16 != 0 || nh % nkv != 0 || nkv > 65535 || mask < 0 || mask > 2 ||
-      (mask != 0 && mask_size <= 0) || nsplit < 1 || nsplit > 65535 || (nsplit > 1 && (part == nullptr || counters == nullptr || span < 1)))
+      (mask != 0 && mask_size <= 0) || nsplit < 1 || nsplit > 65535 || (nsplit > 1 && (part == nullptr || span < 1)))
     return (int)cudaErrorInvalidValue;
   if ((q_stride % 8) != 0 || (out_stride % 8) != 0) return (int)cudaErrorInvalidValue;
   AttnShapedParams p;
@@ -545,7 +531,6 @@ extern "C" int ll_attn_shaped(void* out, long out_stride, const void* q, long q_
   p.nsplit = nsplit;
   p.span = span;
   p.part = part;
-  p.counters = counters;
   dim3 grid(row_blocks, nkv, nsplit);
 #define AS_LAUNCH(HD_, VD_, MIX_)                                                                                  \
   do {                                                                                                             \
@@ -564,5 +549,11 @@ extern "C" int ll_attn_shaped(void* out, long out_stride, const void* q, long q_
   else AS_PICK(false);
 #undef AS_PICK
 #undef AS_LAUNCH
+  int rc = LL_LAUNCH_RESULT();
+  if (rc != 0 || nsplit == 1) return rc;
+  // the rows of the single tokens: row_blocks counts ceil(group / 128) blocks an entry here
+  dim3 jgrid(n_entries, nh);
+  if (vd == 64) ll_launch(attn_shaped_join_kernel<64>, jgrid, dim3(64), 0, stream, p);
+  else ll_launch(attn_shaped_join_kernel<128>, jgrid, dim3(128), 0, stream, p);
   return LL_LAUNCH_RESULT();
 }

@@ -1663,9 +1663,6 @@ def attn_shaped_blocks(q_lens, group: int) -> int:
     return sum((int(n) * group + 127) // 128 for n in q_lens)
 
 
-_attn_shaped_counters = {}
-
-
 def attn_shaped(out: torch.Tensor, q: torch.Tensor, q_stride: int, mixed: bool, gate: Optional[torch.Tensor],
                 temperature: Optional[torch.Tensor], k_cache: torch.Tensor, v_cache: torch.Tensor,
                 block_table: torch.Tensor, cu_q: torch.Tensor, ctx_len: torch.Tensor, req_slot: torch.Tensor,
@@ -1676,8 +1673,8 @@ def attn_shaped(out: torch.Tensor, q: torch.Tensor, q_stride: int, mixed: bool, 
     head sizes 64 and 128.  ``q``: the projection's rows (head h at h * head_dim), or with ``mixed`` the wider
     queries that ``qkv_norm_rotate_store`` leaves for mixed heads (then ``temperature`` is inside them).
     ``nsplit`` > 1 (every entry brings one token): the keys of a row are cut into parts of ``span`` stages of 64
-    keys, each a CTA; the one of a row block that finishes last joins them (counters kept by this module, zero
-    between launches); nsplit * span must cover the stages any token sees.  One launch."""
+    keys, each a CTA, joined by a second kernel; nsplit * span must cover the stages any token sees.  Launches one
+    kernel, two with ``nsplit`` > 1."""
     _need_cuda(out, q, gate, temperature, k_cache, v_cache, block_table, cu_q, ctx_len, req_slot)
     for t, nm in ((block_table, "block_table"), (cu_q, "cu_q"), (ctx_len, "ctx_len"), (req_slot, "req_slot")):
         _i32(t, nm)
@@ -1696,14 +1693,10 @@ def attn_shaped(out: torch.Tensor, q: torch.Tensor, q_stride: int, mixed: bool, 
     _need(temperature is None or temperature.numel() == num_heads, "temperature: a number a head")
     _need(gate is None or (gate.dtype == q.dtype and gate.stride(1) == 1), "gate: [tokens, heads] rows")
     _need(mask == "causal" or (mask_size or 0) > 0, "a window or chunks need a size")
-    part = counters = None
+    part = None
     if nsplit > 1:
         part = torch.empty((out.shape[0], num_heads, nsplit, value_head_dim + 2), dtype=torch.float32,
                            device=out.device)
-        counters = _attn_shaped_counters.get(out.device)
-        if counters is None or counters.numel() < row_blocks * num_kv_heads:
-            counters = torch.zeros(max(row_blocks * num_kv_heads, 4096), dtype=torch.int32, device=out.device)
-            _attn_shaped_counters[out.device] = counters
     load_library("attn_shaped").call(
         "ll_attn_shaped", _ptr(out), c_long(out.stride(0)), _ptr(q), c_long(q_stride), c_int(1 if mixed else 0),
         _ptr(gate), c_long(0 if gate is None else gate.stride(0)), _ptr(temperature), _ptr(k_cache), _ptr(v_cache),
@@ -1711,7 +1704,7 @@ def attn_shaped(out: torch.Tensor, q: torch.Tensor, q_stride: int, mixed: bool, 
         c_int(num_entries), c_int(row_blocks), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim),
         c_int(value_head_dim), c_int(page_size), c_int(k_cache.shape[0]), c_int(ATTN_MASK[mask]),
         c_int(int(mask_size or 0)), c_int(1 if sink else 0), c_float(scale), c_int(nsplit), c_int(span), _ptr(part),
-        _ptr(counters), _ptr(status), _stream())
+        _ptr(status), _stream())
 
 
 def attention_modulated(out: torch.Tensor, q: torch.Tensor, q_stride: int, gate: Optional[torch.Tensor],
