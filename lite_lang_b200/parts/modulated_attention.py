@@ -192,8 +192,9 @@ class ModulatedAttention(Mixer):
 
     def attend_shaped(self, out, proj, mixed_q, step, cache, temperature) -> None:
         """Tensor cores.  Single-token entries come first in a step: their keys are cut into parts of one or more
-        stages of 64 keys, a CTA each (how many follows from the mask's size, so a position's sums keep their
-        order); the portions of prompts after them share the keys among 128 rows a CTA.  Portions whose scores are
+        stages of 64 keys, a CTA each (as many parts as the step's single tokens leave SMs for, so the order of a
+        position's sums depends on how many tokens decode together, within rounding); the portions of prompts after
+        them share the keys among 128 rows a CTA.  Portions whose scores are
         plain by now (no mixed heads, no sink, causal or a window, values as wide as keys; a temperature is on the
         queries already) go to the tcgen05 kernel of the plain attention, which takes the head gate."""
         q = proj if mixed_q is None else mixed_q
@@ -209,7 +210,11 @@ class ModulatedAttention(Mixer):
                 stages = (int(step.max_kv_len) + 63) // 64 + 1
             else:
                 stages = (self.mask_size + 62) // 64 + 1
-            span = (stages + 31) // 32
+            # as many parts as give every SM a CTA, at most one part a stage and 32 parts: 8 tokens on 2 kv heads
+            # with a window of 512 get 9 parts of one stage; 64 tokens one part each (and no join)
+            ctas = n_single * self.num_kv_heads * ((group + 127) // 128)
+            want = max(1, min(32, ops.sm_count(out.device) // ctas))
+            span = (stages + want - 1) // want
             nsplit = (stages + span - 1) // span
             ops.attn_shaped(*head, step.cu_q, step.ctx_len, step.req_slot, n_single, n_single * ((group + 127) // 128),
                             *tail, nsplit=nsplit, span=span)
