@@ -9,7 +9,9 @@ lives in ``cache/storage.py`` and mirrors what is decided here.
 Groups.  Mixers with equal needs (kv heads, head size, window) share a *group*:
 one pool of pages and one block table per request.  A group with a window gives
 pages back as soon as every position in them lies before the window of the
-request's next token; a group without one keeps them until the request ends.
+request's next token (but for the pages of the request's first ``keep_first``
+positions, if the mixers keep those visible); a group without one keeps them
+until the request ends.
 Beside the paged groups there are *state* groups: one record of fixed size per
 request slot, for mixers whose memory does not grow with the sequence.
 
@@ -71,6 +73,7 @@ class PagedGroupSpec:
     planes: int                 # cache planes (one per run-step that writes into this group)
     value_head_dim: Optional[int] = None   # width of a value; None: head_dim; 0: the group has no value plane
     chunk: Optional[int] = None            # a token reads positions of its own chunk of this many only
+    keep_first: int = 0                    # positions below this stay readable whatever the window or chunk
 
     kind = "paged"
 
@@ -100,7 +103,11 @@ class PagedGroupSpec:
         if not self.releases:
             return full
         reach = min(x for x in (self.window, self.chunk) if x is not None)
-        return min(full, (reach + step_tokens + page_size - 1) // page_size + 1)
+        return min(full, (reach + step_tokens + page_size - 1) // page_size + 1 + self.kept_pages(page_size))
+
+    def kept_pages(self, page_size: int) -> int:
+        """The request's first pages that are never given back while it lives (they hold kept positions)."""
+        return (self.keep_first + page_size - 1) // page_size if self.keep_first > 0 else 0
 
 
 @dataclass(frozen=True)
@@ -278,7 +285,8 @@ class CacheManager:
             first_live_page = self.groups[g].first_needed(new_length) // self.page_size
             if first_live_page > req.first_live[g]:
                 gone = []
-                for lp in range(req.first_live[g], min(first_live_page, len(req.pages[g]))):
+                kept = self.groups[g].kept_pages(self.page_size)     # the first pages stay with the request
+                for lp in range(max(req.first_live[g], kept), min(first_live_page, len(req.pages[g]))):
                     if req.pages[g][lp] >= 0:
                         gone.append(req.pages[g][lp])
                         req.pages[g][lp] = -1

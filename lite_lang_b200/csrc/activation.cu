@@ -150,11 +150,12 @@ extern "C" int ll_softcap(float* z, long total, float cap, cudaStream_t stream) 
 
 // ---------------------------------------------------------------------------------------------------------
 // Activation of a plain (ungated) feed-forward, in place: x <- act(x), float32, rounded once.
-// act 0: gelu in its tanh form, 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))); 1: ReLU; 2: SiLU.
+// act 0: gelu in its tanh form, 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))); 1: ReLU; 2: SiLU; 3: ReLU squared.
 // ---------------------------------------------------------------------------------------------------------
 __device__ __forceinline__ float row_activation(float z, int act) {
   if (act == 1) return fmaxf(z, 0.f);
   if (act == 2) return z / (1.0f + expf(-z));
+  if (act == 3) return fmaxf(z, 0.f) * fmaxf(z, 0.f);
   return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
 
@@ -186,7 +187,7 @@ __global__ void act_rows_bf16x8_kernel(bf16* __restrict__ x, long total8, int ac
 
 extern "C" int ll_act_rows(int dtype, void* x, long total, int act, cudaStream_t stream) {
   if (total <= 0) return 0;
-  if (act < 0 || act > 2) return (int)cudaErrorInvalidValue;
+  if (act < 0 || act > 3) return (int)cudaErrorInvalidValue;
   const long most = (long)silu_device_sms() * 16;
   if (dtype == LL_DTYPE_BF16 && (total % 8) == 0 && ((uintptr_t)x % 16) == 0) {
     const int blocks = (int)min((total / 8 + 255) / 256, most);

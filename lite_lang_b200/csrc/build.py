@@ -48,6 +48,7 @@ LIBRARIES: Dict[str, Tuple[Tuple[str, ...], Tuple[str, ...]]] = {
     "moe": (("moe.cu",), ()),
     "streams": (("streams.cu",), ()),
     "linear_attn": (("linear_attention.cu",), ()),
+    "ssd": (("ssd.cu",), ()),
     "attn_mod": (("qkv_norm_rotate_store.cu", "attention_modulated.cu"), ()),
     "attn_shaped": (("attention_shaped_mma.cu",), ()),
 }

@@ -173,7 +173,7 @@ struct GpParams {
   int m_tiles;      // tiles of 256 tokens
   int tiles;        // m_tiles x column tiles (plain: 256 features a tile, gated: 128)
   int vec_ok;       // the output takes 16-byte pieces (aligned base and stride, N a multiple of 8)
-  int act;          // gated: 0 silu(gate) * up, 1 relu(gate) * up; plain: 0 none, 1 gelu (tanh form), 2 ReLU, 3 SiLU
+  int act;          // gated: 0 silu(gate) * up, 1 relu(gate) * up; plain: 0 none, 1 gelu (tanh form), 2 ReLU, 3 SiLU, 4 ReLU squared
   int* status;
   // q|k|v mode only: what follows the projection (N = (nh + 2 nkv) hd; out is q [M, nh hd])
   const float* bias;      // float32 [N] or null
@@ -524,6 +524,8 @@ gemm_pair_kernel(const GpParams p, const __grid_constant__ CUtensorMap wmap, con
                 const float z = __bfloat162float(__float2bfloat16_rn(v[i]));
                 if (p.act == 2) {
                   v[i] = fmaxf(z, 0.f);
+                } else if (p.act == 4) {
+                  v[i] = fmaxf(z, 0.f) * fmaxf(z, 0.f);
                 } else {
                   const float u = p.act == 3 ? z : 1.5957691216057308f * (z + 0.044715f * z * z * z);
                   v[i] = __fdividef(z, 1.0f + __expf(-u));
@@ -674,7 +676,7 @@ extern "C" int ll_gemm_pair(void* out, long out_stride, const void* x, long x_st
 extern "C" int ll_gemm_pair_act(void* out, long out_stride, const void* x, long x_stride, const void* w, int M, int N,
                                 int K, int act, int sm_count, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
-  if (K <= 0 || (K % 8) != 0 || (x_stride % 8) != 0 || sm_count < 2 || act < 0 || act > 3)
+  if (K <= 0 || (K % 8) != 0 || (x_stride % 8) != 0 || sm_count < 2 || act < 0 || act > 4)
     return (int)cudaErrorInvalidValue;
   GpParams p;
   p.out = reinterpret_cast<bf16*>(out);

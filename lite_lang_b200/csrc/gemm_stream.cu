@@ -141,6 +141,7 @@ __device__ __forceinline__ float gt_row_act(float acc, int act) {
   const float z = __bfloat162float(__float2bfloat16_rn(acc));
   if (act == 2) return fmaxf(z, 0.f);
   if (act == 3) return z / (1.0f + expf(-z));
+  if (act == 4) return fmaxf(z, 0.f) * fmaxf(z, 0.f);
   const float u = 0.7978845608028654f * (z + 0.044715f * z * z * z);
   return z / (1.0f + expf(-2.0f * u));
 }
@@ -154,7 +155,7 @@ struct GtParams {
   int ksplit;   // parts the k range is cut into; > 1: out is float32 [ksplit, M, N] partial sums
   int cpp;      // k chunks (stages) per part
   int act;      // GATED: 0 silu(gate) * up, 1 relu(gate) * up
-  int row_act;  // WIDE to bfloat16 with k whole: 0 none; 1 gelu (tanh form), 2 ReLU, 3 SiLU on the result, which is
+  int row_act;  // WIDE to bfloat16 with k whole: 0 none; 1 gelu (tanh form), 2 ReLU, 3 SiLU, 4 ReLU squared on the result, which is
                 // rounded to bfloat16 first, as a product followed by an activation kernel would have it
   // QKV_ROPE only: what follows the projection
   const float* bias;       // float32 [(nh + 2 nkv) hd] or null
@@ -679,7 +680,7 @@ extern "C" int ll_gemm_stream(void* out, long out_stride, int out_f32, const voi
   const int act = (mode >> 8) & 0xff;        // (bits 8..15: the gated mode's activation, 0 SiLU, 1 ReLU)
   const int row_act = (mode >> 16) & 0xff;   // (bits 16..23: an activation on the wide mode's result, see GtParams)
   mode &= 0xff;
-  if (row_act != 0 && (mode != GT_MODE_WIDE || out_f32 || ksplit != 1 || row_act > 3)) return (int)cudaErrorInvalidValue;
+  if (row_act != 0 && (mode != GT_MODE_WIDE || out_f32 || ksplit != 1 || row_act > 4)) return (int)cudaErrorInvalidValue;
   if (M > 64 || K <= 0 || (x_stride % 8) != 0 || sm_count <= 0 || ksplit < 1) return (int)cudaErrorInvalidValue;
   // (33 to 64 tokens: units of 16 features to bfloat16 only, in two blocks of tokens)
   if (M > 32 && (mode != GT_MODE_NARROW || out_f32 || ksplit != 1)) return (int)cudaErrorInvalidValue;

@@ -23,14 +23,17 @@
 // every sum depends on the position only, not on how the tokens were cut into steps or batched.
 #include "common.cuh"
 
-// proj row t: q heads at q_off, head h's rotated part at q_off + h * (d + r) + d; the latent at kv_off (R wide),
-// then the rotated key part (r wide).
+// qsrc row t (row stride q_stride; the projection itself, or the output of a second product when the queries go
+// through a latent of their own): q heads at q_off, head h's rotated part at q_off + h * (d + r) + d; proj row t:
+// the latent at kv_off (R wide), then the rotated key part (r wide).  Both cos and sin are multiplied by
+// `amplitude` (a scaled rotation's factor; 1 otherwise).
 template <typename T>
 __global__ void __launch_bounds__(128)
 latent_prepare_kernel(const T* __restrict__ proj, long proj_stride, int q_off, int kv_off, const float* __restrict__ norm_w,
                       float eps, const float* __restrict__ freq, int rot_dims, const int* __restrict__ positions,
                       const int* __restrict__ slot_map, T* __restrict__ cache, long num_slots,
-                      T* __restrict__ q_full, int H, int d, int r, int R, int* status) {
+                      T* __restrict__ q_full, int H, int d, int r, int R, int* status, float amplitude,
+                      const T* __restrict__ qsrc, long q_stride) {
   __shared__ float scratch[32];
   LL_PDL_TRIGGER();
   LL_PDL_WAIT();
@@ -41,11 +44,13 @@ latent_prepare_kernel(const T* __restrict__ proj, long proj_stride, int q_off, i
   const int half = rot_dims / 2;
   for (int i = tid; i < H * r; i += blockDim.x) {
     const int h = i / r, j = i % r;
-    const T* src = row + q_off + (size_t)h * (d + r) + d;
+    const T* src = qsrc + (size_t)t * q_stride + q_off + (size_t)h * (d + r) + d;
     float out;
     if (j < 2 * half) {
       float sn, cs;
       sincosf(p * freq[j >> 1], &sn, &cs);
+      sn *= amplitude;
+      cs *= amplitude;
       const float u = to_f32<T>(src[j & ~1]), v = to_f32<T>(src[j | 1]);
       out = (j & 1) ? v * cs + u * sn : u * cs - v * sn;
     } else {
@@ -74,6 +79,8 @@ latent_prepare_kernel(const T* __restrict__ proj, long proj_stride, int q_off, i
     if (j < 2 * half) {
       float sn, cs;
       sincosf(p * freq[j >> 1], &sn, &cs);
+      sn *= amplitude;
+      cs *= amplitude;
       const float u = to_f32<T>(lat[R + (j & ~1)]), v = to_f32<T>(lat[R + (j | 1)]);
       out = (j & 1) ? v * cs + u * sn : u * cs - v * sn;
     } else {
@@ -97,7 +104,8 @@ latent_attention_kernel(T* __restrict__ out, const T* __restrict__ q, const T* _
                         const int* __restrict__ block_table, int bt_stride, const int* __restrict__ token_req,
                         const int* __restrict__ req_slot, const int* __restrict__ positions, int first, int H, int R,
                         int r, int page_size, int num_pages, int window, float scale, int* status,
-                        int tiles_per_split, float* __restrict__ part_acc, float* __restrict__ part_ml) {
+                        int tiles_per_split, float* __restrict__ part_acc, float* __restrict__ part_ml,
+                        const float* __restrict__ sink) {
   extern __shared__ float smem[];
   __shared__ long base_s[LA_TK];
   LL_PDL_TRIGGER();
@@ -274,7 +282,8 @@ latent_attention_kernel(T* __restrict__ out, const T* __restrict__ q, const T* _
   for (int i = 0; i < LA_GH / LA_WARPS; ++i) {
     const int g = warp + i * LA_WARPS;
     if (g < hc && lane == 0) {
-      l_s[g] = l_run[i];
+      // the key without a value: one more term of the sum (with splits the merge adds it)
+      l_s[g] = (sink && nsplit == 1) ? l_run[i] + expf(sink[h0 + g] - m_run[i]) : l_run[i];
       if (nsplit > 1) {
         pm[(size_t)g * nsplit * 2] = m_run[i];
         pm[(size_t)g * nsplit * 2 + 1] = l_run[i];
@@ -303,7 +312,7 @@ latent_attention_kernel(T* __restrict__ out, const T* __restrict__ q, const T* _
 template <typename T>
 __global__ void __launch_bounds__(128)
 latent_merge_kernel(T* __restrict__ out, const float* __restrict__ part_acc, const float* __restrict__ part_ml,
-                    int pairs, int R, int nsplit) {
+                    int pairs, int R, int nsplit, const float* __restrict__ sink, int H) {
   __shared__ float w_s[LA_MAX_SPLIT];
   __shared__ float inv_s;
   LL_PDL_TRIGGER();
@@ -313,11 +322,14 @@ latent_merge_kernel(T* __restrict__ out, const float* __restrict__ part_acc, con
   const float* ml = part_ml + (size_t)pair * nsplit * 2;
   if (tid < 32) {
     float m = tid < nsplit ? ml[2 * tid] : -INFINITY;
-    const float M = warp_max(m);
+    float M = warp_max(m);
+    const float sk = sink ? sink[pair % H] : -INFINITY;
+    M = fmaxf(M, sk);
     const float w = (tid < nsplit && m != -INFINITY) ? expf(m - M) : 0.f;
     w_s[tid] = w;
     float L = 0.f;
     for (int s = 0; s < nsplit; ++s) L = fmaf(__shfl_sync(0xffffffffu, w, s), ml[2 * s + 1], L);   // split order
+    if (sink) L += expf(sk - M);
     if (tid == 0) inv_s = L > 0.f ? 1.0f / L : 0.f;
   }
   __syncthreads();
@@ -360,7 +372,7 @@ __global__ void latent_gather_kernel(T* __restrict__ dst, const T* __restrict__ 
 template <typename T>
 __global__ void __launch_bounds__(256)
 latent_masked_softmax_kernel(T* __restrict__ P, const float* __restrict__ S, int rows, int n_keys, int H, int p0, int lo,
-                             int window, float scale) {
+                             int window, float scale, const float* __restrict__ sink) {
   __shared__ float scratch[32];
   LL_PDL_TRIGGER();
   LL_PDL_WAIT();
@@ -372,9 +384,11 @@ latent_masked_softmax_kernel(T* __restrict__ P, const float* __restrict__ S, int
   float m = -INFINITY;
   for (int j = first + threadIdx.x; j <= last; j += blockDim.x) m = fmaxf(m, s[j] * scale);
   m = block_max(m, scratch);
+  if (sink) m = fmaxf(m, sink[i % H]);        // the key without a value: in the denominator only
   float sum = 0.f;
   for (int j = first + threadIdx.x; j <= last; j += blockDim.x) sum += expf(s[j] * scale - m);
   sum = block_sum(sum, scratch);
+  if (sink) sum += expf(sink[i % H] - m);
   const float inv = 1.0f / sum;
   for (int j = threadIdx.x; j < n_keys; j += blockDim.x)
     out[j] = from_f32<T>((j >= first && j <= last) ? expf(s[j] * scale - m) * inv : 0.f);
@@ -383,12 +397,14 @@ latent_masked_softmax_kernel(T* __restrict__ P, const float* __restrict__ S, int
 extern "C" int ll_latent_prepare(int dtype, const void* proj, long proj_stride, int q_off, int kv_off,
                                  const float* norm_w, float eps, const float* freq, int rot_dims, const int* positions,
                                  const int* slot_map, void* cache, long num_slots, void* q_full, int num_tokens, int H,
-                                 int d, int r, int R, int* status, cudaStream_t stream) {
+                                 int d, int r, int R, int* status, float amplitude, const void* qsrc, long q_stride,
+                                 cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   if (H <= 0 || d < 0 || r < 0 || R <= 0 || rot_dims < 0 || rot_dims > r) return (int)cudaErrorInvalidValue;
   LL_DISPATCH_DTYPE(dtype, ll_launch(latent_prepare_kernel<T>, dim3(num_tokens), dim3(128), 0, stream, (const T*)proj,
                                      proj_stride, q_off, kv_off, norm_w, eps, freq, rot_dims, positions, slot_map,
-                                     (T*)cache, num_slots, (T*)q_full, H, d, r, R, status));
+                                     (T*)cache, num_slots, (T*)q_full, H, d, r, R, status, amplitude,
+                                     (const T*)qsrc, q_stride));
   return LL_LAUNCH_RESULT();
 }
 
@@ -396,7 +412,7 @@ extern "C" int ll_latent_attention(int dtype, void* out, const void* q, const vo
                                    int bt_stride, const int* token_req, const int* req_slot, const int* positions,
                                    int first, int num_tokens, int H, int R, int r, int page_size, int num_pages,
                                    int window, float scale, int* status, int nsplit, int tiles_per_split,
-                                   float* part_acc, float* part_ml, cudaStream_t stream) {
+                                   float* part_acc, float* part_ml, const float* sink, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   if (H <= 0 || R <= 0 || R > LA_MAX_R || r < 0 || page_size <= 0 || nsplit < 1) return (int)cudaErrorInvalidValue;
   if (nsplit > 32 || (nsplit > 1 && (tiles_per_split < 1 || part_acc == nullptr || part_ml == nullptr)))
@@ -409,11 +425,11 @@ extern "C" int ll_latent_attention(int dtype, void* out, const void* q, const vo
       cudaFuncSetAttribute(latent_attention_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     ll_launch(latent_attention_kernel<T>, grid, dim3(LA_THREADS), smem, stream, (T*)out, (const T*)q, (const T*)cache,
               block_table, bt_stride, token_req, req_slot, positions, first, H, R, r, page_size, num_pages, window,
-              scale, status, tiles_per_split, part_acc, part_ml);
+              scale, status, tiles_per_split, part_acc, part_ml, sink);
     if (nsplit > 1) {
       const int pairs = num_tokens * H;
       ll_launch(latent_merge_kernel<T>, dim3(pairs), dim3(128), 0, stream, (T*)out + (size_t)first * H * R,
-                (const float*)part_acc, (const float*)part_ml, pairs, R, nsplit);
+                (const float*)part_acc, (const float*)part_ml, pairs, R, nsplit, sink, H);
     }
   });
   return LL_LAUNCH_RESULT();
@@ -428,9 +444,9 @@ extern "C" int ll_latent_gather(int dtype, void* dst, const void* cache, const i
 }
 
 extern "C" int ll_latent_masked_softmax(int dtype, void* P, const float* S, int rows, int n_keys, int H, int p0, int lo,
-                                        int window, float scale, cudaStream_t stream) {
+                                        int window, float scale, const float* sink, cudaStream_t stream) {
   if (rows <= 0) return 0;
   LL_DISPATCH_DTYPE(dtype, ll_launch(latent_masked_softmax_kernel<T>, dim3(rows), dim3(256), 0, stream, (T*)P, S, rows,
-                                     n_keys, H, p0, lo, window, scale));
+                                     n_keys, H, p0, lo, window, scale, sink));
   return LL_LAUNCH_RESULT();
 }

@@ -15,6 +15,11 @@
 // (the exchange adds the same pairs whatever the token's place among the 16), so a position's result is the
 // same bits however the tokens were cut into steps.
 //
+// The same scan serves a state-space layer whose decay and step size differ from token to token
+// (S_t = a_t,h S_(t-1) + dt_t,h k_t v_t^T, o_t = S_t^T q_t + D_h v_t, q and k shared by the `hpg` heads of a
+// group): `tok_decay` and `tok_scale` [tokens, H] replace the constant decay and scale the written values,
+// `skip` [H] adds the token's own value to its read-out.
+//
 // `linear_attn_out`: y = o / rms(o over all heads) * weight * sigmoid(gate), in the engine's dtype.
 #include "common.cuh"
 
@@ -53,7 +58,8 @@ __global__ void __launch_bounds__(LA_THREADS)
 decay_scan_kernel(const T* __restrict__ proj, long stride, int q_off, int k_off, int v_off,
                   const float* __restrict__ decay, float* __restrict__ state, long slot_stride, int num_slots,
                   const int* __restrict__ cu_q, const int* __restrict__ req_slot, float* __restrict__ o, int H, int dk,
-                  int dv, int write_state, int* status) {
+                  int dv, int write_state, int* status, int hpg, const float* __restrict__ tok_decay,
+                  const float* __restrict__ tok_scale, const float* __restrict__ skip) {
   constexpr int DKP = R * LA_LANES;
   constexpr int VN = LaVec<T>::N;
   constexpr int ROWV = DKP / VN;                                      // 16-byte pieces of a (padded) q or k row
@@ -61,11 +67,14 @@ decay_scan_kernel(const T* __restrict__ proj, long stride, int q_off, int k_off,
   __shared__ __align__(16) float qs[LA_CHUNK * DKP];
   __shared__ __align__(16) float ks[LA_CHUNK * DKP];
   __shared__ float vs[LA_CHUNK * LA_COLS];
+  __shared__ float ds[LA_CHUNK], ws[LA_CHUNK];     // a token's decay and the factor on what it writes
   LL_PDL_TRIGGER();
   const int cg = blockIdx.x, h = blockIdx.y, e = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & (LA_LANES - 1), cl = tid / LA_LANES;
   const int col = cg * LA_COLS + cl;
-  const float d = decay[h];
+  const float d_head = decay ? decay[h] : 1.f;
+  const float skip_h = skip ? skip[h] : 0.f;
+  const int hq = h / hpg;                        // the head whose q and k this head reads
   LL_PDL_WAIT();
   const int t0 = cu_q[e], t1 = cu_q[e + 1];
   const int slot = req_slot[e];
@@ -92,7 +101,7 @@ decay_scan_kernel(const T* __restrict__ proj, long stride, int q_off, int k_off,
 
   // ---- staging: ask for a chunk's rows (registers), later put them into shared memory as float32 ----
   uint4 raw[VEC ? NV : 1];
-  float vraw = 0.f;
+  float vraw = 0.f, draw = 1.f, wraw = 1.f;
   auto ask = [&](int base) {
     const int n = min(LA_CHUNK, t1 - base);
     if (VEC) {
@@ -103,11 +112,15 @@ decay_scan_kernel(const T* __restrict__ proj, long stride, int q_off, int k_off,
         const int t = rem / ROWV, c = (rem - t * ROWV) * VN;
         raw[u] = make_uint4(0, 0, 0, 0);
         if (which < 2 && t < n && c < dk)
-          raw[u] = *reinterpret_cast<const uint4*>(proj + (size_t)(base + t) * stride + (which ? k_off : q_off) + h * dk + c);
+          raw[u] = *reinterpret_cast<const uint4*>(proj + (size_t)(base + t) * stride + (which ? k_off : q_off) + hq * dk + c);
       }
     }
     const int t = tid / LA_COLS, c = cg * LA_COLS + (tid - t * LA_COLS);
     vraw = (t < n && c < dv) ? to_f32<T>(proj[(size_t)(base + t) * stride + v_off + h * dv + c]) : 0.f;
+    if (tid < LA_CHUNK) {
+      draw = (tok_decay && tid < n) ? tok_decay[(size_t)(base + tid) * H + h] : d_head;
+      wraw = (tok_scale && tid < n) ? tok_scale[(size_t)(base + tid) * H + h] : 1.f;
+    }
   };
   auto put = [&](int base) {
     const int n = min(LA_CHUNK, t1 - base);
@@ -133,11 +146,15 @@ decay_scan_kernel(const T* __restrict__ proj, long stride, int q_off, int k_off,
         const int t = i / DKP, c = i - t * DKP;
         const bool in = t < n && c < dk;
         const T* row = proj + (size_t)(base + (in ? t : 0)) * stride;
-        qs[i] = in ? to_f32<T>(row[q_off + h * dk + c]) : 0.f;
-        ks[i] = in ? to_f32<T>(row[k_off + h * dk + c]) : 0.f;
+        qs[i] = in ? to_f32<T>(row[q_off + hq * dk + c]) : 0.f;
+        ks[i] = in ? to_f32<T>(row[k_off + hq * dk + c]) : 0.f;
       }
     }
     vs[tid] = vraw;
+    if (tid < LA_CHUNK) {
+      ds[tid] = draw;
+      ws[tid] = wraw;
+    }
   };
 
   if (t0 < t1) ask(t0);
@@ -152,7 +169,9 @@ decay_scan_kernel(const T* __restrict__ proj, long stride, int q_off, int k_off,
     for (int t = 0; t < LA_CHUNK; ++t) {
       part[t] = 0.f;
       if (t < n) {
-        const float v = vs[t * LA_COLS + cl];
+        const float v0 = vs[t * LA_COLS + cl];
+        const float v = v0 * ws[t];
+        const float d = ds[t];
         float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
         for (int j = 0; j < R / 4; ++j) {
@@ -168,6 +187,7 @@ decay_scan_kernel(const T* __restrict__ proj, long stride, int q_off, int k_off,
           a3 = fmaf(S[4 * j + 3], q4.w, a3);
         }
         part[t] = (a0 + a1) + (a2 + a3);
+        if (lane == 0) part[t] = fmaf(skip_h, v0, part[t]);      // (one lane of the column: the exchange sums the lanes)
       }
     }
     // sums over the 16 lanes of a column for the 16 tokens at once: after the exchange lane l holds token l's
@@ -312,9 +332,11 @@ linear_attn_out_kernel(T* __restrict__ y, const float* __restrict__ o, const flo
 extern "C" int ll_decay_scan(int dtype, const void* proj, long stride, int q_off, int k_off, int v_off,
                              const float* decay, float* state, long slot_stride, int num_slots, const int* cu_q,
                              const int* req_slot, float* o, int num_entries, int H, int dk, int dv, int write_state,
-                             int* status, cudaStream_t stream) {
+                             int* status, int hpg, const float* tok_decay, const float* tok_scale, const float* skip,
+                             cudaStream_t stream) {
   if (num_entries <= 0) return 0;
-  if (H <= 0 || dk <= 0 || dk > 256 || dv <= 0) return (int)cudaErrorInvalidValue;
+  if (H <= 0 || dk <= 0 || dk > 256 || dv <= 0 || hpg <= 0 || H % hpg != 0 || (decay == nullptr && tok_decay == nullptr))
+    return (int)cudaErrorInvalidValue;
   const int need = (dk + LA_LANES - 1) / LA_LANES;
   const int R = need <= 4 ? 4 : need <= 8 ? 8 : 16;
   dim3 grid((dv + LA_COLS - 1) / LA_COLS, H, num_entries);
@@ -323,7 +345,8 @@ extern "C" int ll_decay_scan(int dtype, const void* proj, long stride, int q_off
                    (dk % ve) == 0;
 #define LA_LAUNCH(RR, VV)                                                                                          \
   ll_launch(decay_scan_kernel<T, RR, VV>, grid, dim3(LA_THREADS), 0, stream, (const T*)proj, stride, q_off, k_off, \
-            v_off, decay, state, slot_stride, num_slots, cu_q, req_slot, o, H, dk, dv, write_state, status)
+            v_off, decay, state, slot_stride, num_slots, cu_q, req_slot, o, H, dk, dv, write_state, status, hpg,   \
+            tok_decay, tok_scale, skip)
   LL_DISPATCH_DTYPE(dtype, {
     if (vec) {
       if (R == 4) LA_LAUNCH(4, true);

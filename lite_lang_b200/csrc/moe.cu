@@ -130,14 +130,21 @@ moe_router_kernel(const T* __restrict__ x, long x_stride, const float* __restric
   }
 }
 
-// act: 0 relu(z)^2, 1 silu(z), 2 gelu_tanh(z).
+// act: 0 relu(z)^2, 1 silu(z), 2 gelu_tanh(z), 3 gelu(z) (the erf form).
 __device__ __forceinline__ float moe_activation(float z, int act) {
   if (act == 0) {
     const float r = fmaxf(z, 0.f);
     return r * r;
   }
   if (act == 1) return z / (1.0f + expf(-z));
+  if (act == 3) return 0.5f * z * (1.0f + erff(z * 0.7071067811865476f));
   return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+// The expert's weight w for the token goes onto the activation's output, act(z) w, or (MOE_ACT_WEIGHT_IN set in
+// `act`) onto its input, act(w z): the expert then works on w times the token's row, since U (w x) = w (U x).
+#define MOE_ACT_WEIGHT_IN 16
+__device__ __forceinline__ float moe_weighted_activation(float z, float w, int act) {
+  return (act & MOE_ACT_WEIGHT_IN) ? moe_activation(z * w, act & 15) : moe_activation(z, act) * w;
 }
 
 // h: T [tokens, shared_ff + E * ff] in place: h = act(h) * weight, weight 1 for the first shared_ff columns,
@@ -172,7 +179,7 @@ __global__ void moe_act_kernel(T* __restrict__ h, const float* __restrict__ gate
       const int c = c0 + u;
       const float w = c < shared_ff ? 1.f : gates[(size_t)t * E + (c - shared_ff) / ff];
       // an expert that was not chosen contributes an exact zero whatever its first product gave
-      v[u] = from_f32<T>(w == 0.f ? 0.f : moe_activation(to_f32<T>(v[u]), act) * w);
+      v[u] = from_f32<T>(w == 0.f ? 0.f : moe_weighted_activation(to_f32<T>(v[u]), w, act));
     }
     if (VEC > 1) {
       *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(v);
@@ -294,7 +301,7 @@ __global__ void moe_row_act_kernel(T* __restrict__ h, const float* __restrict__ 
     if (VEC > 1) *reinterpret_cast<uint4*>(v) = reinterpret_cast<const uint4*>(h)[idx];
     else v[0] = h[idx];
 #pragma unroll
-    for (int u = 0; u < VEC; ++u) v[u] = from_f32<T>(moe_activation(to_f32<T>(v[u]), act) * w);
+    for (int u = 0; u < VEC; ++u) v[u] = from_f32<T>(moe_weighted_activation(to_f32<T>(v[u]), w, act));
     if (VEC > 1) reinterpret_cast<uint4*>(h)[idx] = *reinterpret_cast<const uint4*>(v);
     else h[idx] = v[0];
   }

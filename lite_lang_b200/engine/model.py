@@ -127,7 +127,8 @@ class CausalLM:
         for need, n in zip(keys, planes):
             if isinstance(need, PagedKVNeed):
                 vd = need.head_dim if need.value_head_dim is None else need.value_head_dim
-                groups.append(PagedGroupSpec(need.num_kv_heads, need.head_dim, need.window, n, vd, need.chunk))
+                groups.append(PagedGroupSpec(need.num_kv_heads, need.head_dim, need.window, n, vd, need.chunk,
+                                             need.keep_first))
             elif isinstance(need, StateNeed):
                 groups.append(StateGroupSpec(tuple(need.shape), need.dtype, n))
             else:

@@ -16,7 +16,7 @@ from __future__ import annotations
 import ctypes
 import os
 from ctypes import c_float, c_int, c_long, c_void_p
-from typing import Optional
+from typing import Optional, Tuple
 
 import torch
 
@@ -1174,10 +1174,15 @@ def delta_out(out: torch.Tensor, o: torch.Tensor, weight: torch.Tensor, gate: to
 # --------------------------------------------------------------------------
 def latent_prepare(proj: torch.Tensor, q_off: int, kv_off: int, norm_w: torch.Tensor, eps: float, freq: torch.Tensor,
                    rot_dims: int, positions: torch.Tensor, slot_map: Optional[torch.Tensor], cache: torch.Tensor,
-                   q_full: torch.Tensor, H: int, d: int, r: int, R: int, status: Optional[torch.Tensor]) -> None:
+                   q_full: torch.Tensor, H: int, d: int, r: int, R: int, status: Optional[torch.Tensor],
+                   amplitude: float = 1.0, q: Optional[torch.Tensor] = None) -> None:
     """Per token: the latent's RMS norm and the rotated key part into the cache row, and every head's rotated
-    query part into ``q_full`` [tokens, H, R + r] behind the R latent-space numbers (which a product fills)."""
-    _need_cuda(proj, norm_w, freq, positions, slot_map, cache, q_full)
+    query part into ``q_full`` [tokens, H, R + r] behind the R latent-space numbers (which a product fills).
+    ``q``: the rows that hold the query heads at ``q_off`` when they are not rows of ``proj`` (queries made by a
+    second product); ``amplitude``: a factor on cos and sin."""
+    _need_cuda(proj, norm_w, freq, positions, slot_map, cache, q_full, q)
+    q = proj if q is None else q
+    _need(q.dtype == proj.dtype and q.stride(1) == 1 and q.shape[0] == proj.shape[0], "latent_prepare: q rows")
     _f32(norm_w, "norm_w")
     _f32(freq, "freq")
     _i32(positions, "positions")
@@ -1190,18 +1195,22 @@ def latent_prepare(proj: torch.Tensor, q_off: int, kv_off: int, norm_w: torch.Te
         "ll_latent_prepare", c_int(_dtype_code(proj)), _ptr(proj), c_long(proj.stride(0)), c_int(q_off), c_int(kv_off),
         _ptr(norm_w), c_float(eps), _ptr(freq), c_int(rot_dims), _ptr(positions), _ptr(slot_map), _ptr(cache),
         c_long(cache.shape[0] * cache.shape[2]), _ptr(q_full), c_int(proj.shape[0]), c_int(H), c_int(d), c_int(r),
-        c_int(R), _ptr(status), _stream())
+        c_int(R), _ptr(status), c_float(amplitude), _ptr(q), c_long(q.stride(0)), _stream())
 
 
 def latent_attention(out: torch.Tensor, q_full: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, step,
                      first: int, count: int, H: int, R: int, r: int, page_size: int, window: Optional[int],
-                     scale: float, nsplit: int = 1, tiles_per_split: int = 0) -> None:
+                     scale: float, nsplit: int = 1, tiles_per_split: int = 0,
+                     sink: Optional[torch.Tensor] = None) -> None:
     """Attention in the latent space for tokens ``first .. first + count - 1`` of the step.  ``q_full``
     [tokens, H, R + r] and ``out`` [tokens, H, R] (sum_j p_j c_j per head) have the cache's dtype.
     ``nsplit`` > 1: every query's keys are shared out over that many CTAs, ``tiles_per_split`` tiles of 32
     positions each (counted from the query's first visible tile; together they must cover the longest run of
-    keys a query of the step sees), and merged by a second kernel."""
-    _need_cuda(out, q_full, cache, block_table)
+    keys a query of the step sees), and merged by a second kernel.  ``sink`` float32 [H]: every head's softmax
+    has one more key of that score, which carries no value."""
+    _need_cuda(out, q_full, cache, block_table, sink)
+    _f32(sink, "sink")
+    _need(sink is None or sink.numel() == H, "latent_attention: sink is a number a head")
     _need(q_full.is_contiguous() and out.is_contiguous() and q_full.dtype == cache.dtype == out.dtype
           and tuple(q_full.shape[1:]) == (H, R + r) and tuple(out.shape[1:]) == (H, R), "latent_attention: layouts")
     _need(R <= 512, f"latent_attention: a latent of {R} numbers is wider than the kernel takes (512)")
@@ -1216,7 +1225,7 @@ def latent_attention(out: torch.Tensor, q_full: torch.Tensor, cache: torch.Tenso
         c_int(block_table.stride(0)), _ptr(step.token_req), _ptr(step.req_slot), _ptr(step.positions), c_int(first),
         c_int(count), c_int(H), c_int(R), c_int(r), c_int(page_size), c_int(cache.shape[0]), c_int(window or 0),
         c_float(scale), _ptr(step.status), c_int(nsplit), c_int(tiles_per_split), _ptr(part_acc), _ptr(part_ml),
-        _stream())
+        _ptr(sink), _stream())
 
 
 def latent_gather(dst: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, slot: int, lo: int, page_size: int,
@@ -1235,7 +1244,7 @@ def latent_gather(dst: torch.Tensor, cache: torch.Tensor, block_table: torch.Ten
 
 
 def latent_masked_softmax(P: torch.Tensor, S: torch.Tensor, H: int, p0: int, lo: int, window: Optional[int],
-                          scale: float) -> None:
+                          scale: float, sink: Optional[torch.Tensor] = None) -> None:
     """P = softmax(scale * S) over the keys each row may see, zero elsewhere.  Row i is query position
     p0 + i // H; column j is key position lo + j; a query at p sees max(lo, p - window + 1) .. p."""
     _need_cuda(P, S)
@@ -1243,7 +1252,7 @@ def latent_masked_softmax(P: torch.Tensor, S: torch.Tensor, H: int, p0: int, lo:
     _need(P.is_contiguous() and tuple(P.shape) == tuple(S.shape), "latent_masked_softmax: shapes")
     load_library("latent_attn").call(
         "ll_latent_masked_softmax", c_int(_dtype_code(P)), _ptr(P), _ptr(S), c_int(S.shape[0]), c_int(S.shape[1]),
-        c_int(H), c_int(p0), c_int(lo), c_int(window or 0), c_float(scale), _stream())
+        c_int(H), c_int(p0), c_int(lo), c_int(window or 0), c_float(scale), _ptr(sink), _stream())
 
 
 def batched_heads(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None,
@@ -1272,7 +1281,8 @@ def product(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None
 # routed feed-forward
 # --------------------------------------------------------------------------
 MOE_SCORE = {"softmax": 0, "sigmoid": 1, "softmax_top": 2}
-MOE_ACT = {"relu2": 0, "silu": 1, "gelu_tanh": 2}
+MOE_ACT = {"relu2": 0, "silu": 1, "gelu_tanh": 2, "gelu": 3}
+MOE_ACT_WEIGHT_IN = 16     # added to an activation's code: the expert's weight multiplies the activation's input
 
 
 def moe_router(x: torch.Tensor, w_router: torch.Tensor, gates: torch.Tensor, top_idx: torch.Tensor,
@@ -1332,14 +1342,17 @@ def moe_row_gated_act(h: torch.Tensor, row_w: Optional[torch.Tensor], limit: flo
     return out
 
 
-def moe_act(h: torch.Tensor, gates: torch.Tensor, shared_ff: int, ff: int, E: int, act: str) -> None:
-    """In place on the first product over all experts' rows: activation times the expert's weight for the token."""
+def moe_act(h: torch.Tensor, gates: torch.Tensor, shared_ff: int, ff: int, E: int, act: str,
+            weight_in: bool = False) -> None:
+    """In place on the first product over all experts' rows: activation times the expert's weight for the token
+    (``weight_in``: the activation of the weight times the unit, i.e. the expert works on the weighted row)."""
     _need_cuda(h, gates)
     _f32(gates, "gates")
     _need(h.stride(1) == 1 and h.stride(0) == h.shape[1] and h.shape[1] == shared_ff + E * ff,
           "moe_act: h is [tokens, shared + experts * ff]")
     load_library("moe").call("ll_moe_act", c_int(_dtype_code(h)), _ptr(h), _ptr(gates), c_int(h.shape[0]),
-                             c_int(shared_ff), c_int(ff), c_int(E), c_int(MOE_ACT[act]), c_int(sm_count(h.device)),
+                             c_int(shared_ff), c_int(ff), c_int(E),
+                             c_int(MOE_ACT[act] + (MOE_ACT_WEIGHT_IN if weight_in else 0)), c_int(sm_count(h.device)),
                              _stream())
 
 
@@ -1373,13 +1386,14 @@ def moe_gather_rows(x: torch.Tensor, row_token: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def moe_row_act(h: torch.Tensor, row_w: torch.Tensor, act: str) -> None:
-    """In place: activation of every row times the row's routing weight."""
+def moe_row_act(h: torch.Tensor, row_w: torch.Tensor, act: str, weight_in: bool = False) -> None:
+    """In place: activation of every row times the row's routing weight (``weight_in``: of the row times it)."""
     _need_cuda(h, row_w)
     _f32(row_w, "row_w")
     _need(h.is_contiguous() and row_w.numel() == h.shape[0], "moe_row_act: layout")
     load_library("moe").call("ll_moe_row_act", c_int(_dtype_code(h)), _ptr(h), _ptr(row_w), c_int(h.shape[0]),
-                             c_int(h.shape[1]), c_int(MOE_ACT[act]), c_int(sm_count(h.device)), _stream())
+                             c_int(h.shape[1]), c_int(MOE_ACT[act] + (MOE_ACT_WEIGHT_IN if weight_in else 0)),
+                             c_int(sm_count(h.device)), _stream())
 
 
 def moe_combine(base: Optional[torch.Tensor], y: torch.Tensor, pair_row: torch.Tensor) -> torch.Tensor:
@@ -1483,22 +1497,79 @@ def silu_rows(x: torch.Tensor) -> None:
                                      c_int(x.shape[0]), c_int(x.shape[1]), c_int(sm_count(x.device)), _stream())
 
 
-def decay_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, decay: torch.Tensor, state: torch.Tensor,
-               step, o: torch.Tensor, H: int, dk: int, dv: int, write_state: bool = True) -> None:
+def decay_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, decay: Optional[torch.Tensor],
+               state: torch.Tensor, step, o: torch.Tensor, H: int, dk: int, dv: int, write_state: bool = True,
+               heads_per_group: int = 1, token_decay: Optional[torch.Tensor] = None,
+               token_scale: Optional[torch.Tensor] = None, skip: Optional[torch.Tensor] = None) -> None:
     """S_t = decay_h S_(t-1) + k_t v_t^T, o_t = S_t^T q_t for every entry's tokens in order; q, k, v are the
-    columns of ``proj`` at the three offsets (already activated); ``state`` float32 [slots, H * dv * dk] goes on
-    from where the request stopped; ``o`` float32 [tokens, H * dv]."""
-    _need_cuda(proj, decay, state, o)
+    columns of ``proj`` at the three offsets (already activated); ``state`` float32 [slots, >= H * dv * dk] goes on
+    from where the request stopped; ``o`` float32 [tokens, H * dv].
+    A state-space layer uses the same scan: ``token_decay`` and ``token_scale`` float32 [tokens, H] give every
+    token's decay and the factor on what it writes (S_t = a_t S_(t-1) + dt_t k_t v_t^T), ``skip`` float32 [H] adds
+    skip_h v_t to the read-out, and the ``heads_per_group`` heads of a group read the same q and k."""
+    _need_cuda(proj, decay, state, o, token_decay, token_scale, skip)
     _f32(decay, "decay")
     _f32(state, "state")
     _f32(o, "o")
-    _need(proj.stride(1) == 1 and dk <= 256 and decay.numel() == H and state.shape[1] == H * dk * dv
-          and o.shape[1] == H * dv, "decay_scan: shapes (key heads of at most 256 channels)")
+    for t_, nm in ((token_decay, "token_decay"), (token_scale, "token_scale"), (skip, "skip")):
+        _f32(t_, nm)
+    _need(decay is not None or token_decay is not None, "decay_scan: a decay a head or a token is needed")
+    _need(all(t_ is None or (t_.is_contiguous() and tuple(t_.shape) == (proj.shape[0], H))
+              for t_ in (token_decay, token_scale)), "decay_scan: token_decay and token_scale are [tokens, H]")
+    _need(proj.stride(1) == 1 and dk <= 256 and (decay is None or decay.numel() == H)
+          and (skip is None or skip.numel() == H) and state.shape[1] >= H * dk * dv
+          and o.shape[1] == H * dv and o.is_contiguous() and H % heads_per_group == 0,
+          "decay_scan: shapes (key heads of at most 256 channels)")
     load_library("linear_attn").call(
         "ll_decay_scan", c_int(_dtype_code(proj)), _ptr(proj), c_long(proj.stride(0)), c_int(q_off), c_int(k_off),
         c_int(v_off), _ptr(decay), _ptr(state), c_long(state.stride(0)), c_int(state.shape[0]), _ptr(step.cu_q),
         _ptr(step.req_slot), _ptr(o), c_int(step.num_entries), c_int(H), c_int(dk), c_int(dv),
+        c_int(1 if write_state else 0), _ptr(step.status), c_int(heads_per_group), _ptr(token_decay),
+        _ptr(token_scale), _ptr(skip), _stream())
+
+
+def ssd_prepare(proj: torch.Tensor, x_off: int, dt_off: int, conv_w: torch.Tensor, conv_b: Optional[torch.Tensor],
+                A_log: torch.Tensor, dt_bias: torch.Tensor, state: torch.Tensor, tail_off: int, step,
+                xbc: torch.Tensor, dt: torch.Tensor, decay: torch.Tensor, write_state: bool = True) -> None:
+    """The pieces of a state-space layer before its scan, a token: the causal convolution (+ bias) and SiLU of the
+    ``C`` channels of ``proj`` at ``x_off`` into ``xbc`` float32 [tokens, C], continuing from the last taps - 1
+    inputs that the request's record holds at ``tail_off``; dt = softplus(proj[dt_off + h] + dt_bias[h]) and
+    decay = exp(-exp(A_log[h]) dt) into float32 [tokens, H].  Then (a second launch) the records' tails are
+    brought up to date.  ``conv_w`` float32 [C, taps]."""
+    _need_cuda(proj, conv_w, conv_b, A_log, dt_bias, state, xbc, dt, decay)
+    for t_, nm in ((conv_w, "conv_w"), (conv_b, "conv_b"), (A_log, "A_log"), (dt_bias, "dt_bias"), (state, "state"),
+                   (xbc, "xbc"), (dt, "dt"), (decay, "decay")):
+        _f32(t_, nm)
+    C, taps = conv_w.shape
+    H = A_log.numel()
+    n = proj.shape[0]
+    _need(proj.stride(1) == 1 and conv_w.is_contiguous() and (conv_b is None or conv_b.numel() == C)
+          and dt_bias.numel() == H and xbc.is_contiguous() and tuple(xbc.shape) == (n, C)
+          and dt.is_contiguous() and decay.is_contiguous() and tuple(dt.shape) == tuple(decay.shape) == (n, H)
+          and state.dim() == 2 and state.stride(1) == 1 and state.shape[1] >= tail_off + (taps - 1) * C,
+          "ssd_prepare: shapes")
+    load_library("ssd").call(
+        "ll_ssd_prepare", c_int(_dtype_code(proj)), _ptr(proj), c_long(proj.stride(0)), c_int(x_off), c_int(dt_off),
+        _ptr(conv_w), _ptr(conv_b), _ptr(A_log), _ptr(dt_bias), _ptr(state), c_long(state.stride(0)), c_long(tail_off),
+        c_int(state.shape[0]), _ptr(step.token_req), _ptr(step.cu_q), _ptr(step.req_slot), _ptr(xbc), _ptr(dt),
+        _ptr(decay), c_int(n), c_int(step.num_entries), c_int(C), c_int(H), c_int(taps),
         c_int(1 if write_state else 0), _ptr(step.status), _stream())
+
+
+def ssd_gated_norm(out: torch.Tensor, y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, eps: float,
+                   parts: int) -> None:
+    """out = u / rms(u) * weight over each of ``parts`` equal parts of the row, u = y * silu(z); ``y`` float32
+    [tokens, width], ``z`` (a view of the projection's rows) and ``out`` in the engine's dtype."""
+    _need_cuda(out, y, z, weight)
+    _f32(y, "y")
+    _f32(weight, "weight")
+    width = y.shape[1]
+    _need(y.is_contiguous() and z.stride(1) == 1 and out.stride(1) == 1 and z.dtype == out.dtype
+          and tuple(z.shape) == tuple(out.shape) == tuple(y.shape) and weight.numel() == width and width % parts == 0,
+          "ssd_gated_norm: shapes")
+    load_library("ssd").call("ll_ssd_gated_norm", c_int(_dtype_code(out)), _ptr(out), c_long(out.stride(0)), _ptr(y),
+                             _ptr(z), c_long(z.stride(0)), _ptr(weight), c_float(eps), c_int(y.shape[0]), c_int(width),
+                             c_int(parts), _stream())
 
 
 def linear_attn_out(y: torch.Tensor, o: torch.Tensor, weight: torch.Tensor, gate: torch.Tensor, eps: float) -> None:
@@ -1554,7 +1625,7 @@ def round_rows(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
     return out
 
 
-ROW_ACT = {"gelu_tanh": 0, "relu": 1, "silu": 2}
+ROW_ACT = {"gelu_tanh": 0, "relu": 1, "silu": 2, "relu2": 3}
 
 
 def linear_act(x: torch.Tensor, weight: torch.Tensor, act: str) -> torch.Tensor:
@@ -1713,13 +1784,27 @@ def attention_modulated(out: torch.Tensor, q: torch.Tensor, q_stride: int, gate:
                         num_heads: int, num_kv_heads: int, head_dim: int, value_head_dim: int, page_size: int,
                         mask: str, mask_size: Optional[int], sink: bool, scale: float,
                         temperature: Optional[torch.Tensor], head_mix: Optional[torch.Tensor],
-                        status: Optional[torch.Tensor]) -> None:
+                        status: Optional[torch.Tensor], sink_values: Optional[torch.Tensor] = None,
+                        distance_bias: Optional[torch.Tensor] = None, keep_first: int = 0,
+                        softcap: Optional[float] = None, query_temperature: Optional[Tuple[float, int]] = None,
+                        gate_channels: bool = False, out_scale: float = 1.0) -> None:
     """Attention of every new token over its request's cached keys with shaped scores (any sizes, both dtypes):
     a number a head on the scores (``temperature``), the heads' scores mixed by ``head_mix`` [nh, nh], a window
     or chunks (``mask``, ``mask_size``), one more key of score 0 without a value (``sink``), a sigmoid gate a
-    head on the output (``gate``: a view whose element [t, h] is token t's gate input of head h, with the row
-    stride of ``q``)."""
-    _need_cuda(out, q, gate, k_cache, v_cache, block_table, token_req, req_slot, positions, temperature, head_mix)
+    head on the output (``gate``: a view whose element [t, h] is token t's gate input of head h).
+    ``sink_values`` float32 [nh]: the score of the key without a value, a head.  ``distance_bias`` float32
+    [distances, nh]: added to the score of a key ``min(n, distances - 1)`` positions back.  ``keep_first``: with a
+    window, the request's first positions stay visible.  ``softcap``: s <- cap tanh(s / cap) before the bias.
+    ``query_temperature`` (coef, every): the scores of the query at position p times
+    1 + coef ln(floor((p + 1) / every) + 1).  ``gate_channels``: ``gate`` is [tokens, nh * vd], a gate a channel.
+    ``out_scale``: a constant on the output, applied before its one rounding."""
+    _need_cuda(out, q, gate, k_cache, v_cache, block_table, token_req, req_slot, positions, temperature, head_mix,
+               sink_values, distance_bias)
+    _f32(sink_values, "sink_values")
+    _f32(distance_bias, "distance_bias")
+    _need(sink_values is None or (sink and sink_values.numel() == num_heads), "sink_values: a number a head")
+    _need(distance_bias is None or (distance_bias.dim() == 2 and distance_bias.shape[1] == num_heads
+                                    and distance_bias.is_contiguous()), "distance_bias is [distances, heads]")
     for t, nm in ((block_table, "block_table"), (token_req, "token_req"), (req_slot, "req_slot"),
                   (positions, "positions")):
         _i32(t, nm)
@@ -1733,12 +1818,18 @@ def attention_modulated(out: torch.Tensor, q: torch.Tensor, q_stride: int, gate:
           and tuple(v_cache.shape[1:]) == (num_kv_heads, page_size, value_head_dim), "cache plane shape")
     _need(temperature is None or temperature.numel() == num_heads, "temperature: a number a head")
     _need(head_mix is None or tuple(head_mix.shape) == (num_heads, num_heads), "head_mix is [heads, heads]")
-    _need(gate is None or (gate.dtype == q.dtype and gate.stride(0) == q_stride and gate.stride(1) == 1),
-          "gate: a view of the projection's rows")
+    _need(gate is None or (gate.dtype == q.dtype and gate.stride(1) == 1
+                           and gate.shape[1] == (num_heads * value_head_dim if gate_channels else num_heads)),
+          "gate: a number a head (or a channel) and token, rows of the projection's dtype")
+    qt_coef, qt_every = (0.0, 0) if query_temperature is None else (float(query_temperature[0]), int(query_temperature[1]))
     load_library("attn_mod").call(
         "ll_attention_modulated", c_int(_dtype_code(out)), _ptr(out), c_long(out.stride(0)), _ptr(q), c_long(q_stride),
         _ptr(gate), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), c_int(block_table.stride(0)), _ptr(token_req),
         _ptr(req_slot), _ptr(positions), c_int(num_tokens), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim),
         c_int(value_head_dim), c_int(page_size), c_int(k_cache.shape[0]), c_int(ATTN_MASK[mask]),
         c_int(int(mask_size or 0)), c_int(1 if sink else 0), c_float(scale), _ptr(temperature), _ptr(head_mix),
-        _ptr(status), _stream())
+        _ptr(status), _ptr(sink_values), _ptr(distance_bias),
+        c_int(0 if distance_bias is None else distance_bias.shape[0]), c_int(int(keep_first or 0)),
+        c_float(float(softcap or 0.0)), c_float(qt_coef), c_int(qt_every),
+        c_long(0 if gate is None else gate.stride(0)), c_int(1 if gate_channels else 0), c_float(out_scale),
+        _stream())

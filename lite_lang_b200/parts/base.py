@@ -51,6 +51,8 @@ class TensorDecl:
     std: Optional[float] = None
     mean: float = 0.0
     eye: float = 0.0               # random weights: this much of the identity is added (square matrices)
+    # random weights: the shape to draw when ``shape`` has a size that only the checkpoint knows
+    random_shape: Optional[Tuple[int, ...]] = None
 
 
 @dataclass(frozen=True)
@@ -68,6 +70,8 @@ class PagedKVNeed:
     value_head_dim: Optional[int] = None   # width of a value; None: head_dim; 0: no value plane
     # a token reads the positions of its own chunk only (chunks of this many positions, counted from 0)
     chunk: Optional[int] = None
+    # with a window: the request's first positions stay readable whatever the window (their pages are kept)
+    keep_first: int = 0
 
 
 @dataclass(frozen=True)

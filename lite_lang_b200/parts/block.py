@@ -38,6 +38,16 @@ class PreNormBlock(Block):
         return h, f
 
 
+class PreNormMixerOnlyBlock(Block):
+    """The pre-norm arrangement of a layer without a feed-forward: h += mixer(norm(h))."""
+
+    roles = {"mixer_norm": "norm", "mixer": "mixer"}
+
+    def forward(self, h, delta, step, caches):
+        x = self.mixer_norm.add_forward(h, delta)
+        return h, self.mixer.forward(x, step, caches["mixer"])
+
+
 class ParallelBlock(Block):
     """Parallel arrangement: with n = norm(h), h += mixer(n) + feed_forward(n).  One norm; both parts read
     its output.  Their outputs are handed on together and added (to each other, then to the residual
@@ -96,6 +106,7 @@ class OutputNormMixerOnlyBlock(OutputNormBlock):
 
 
 register_part("block", "pre_norm", PreNormBlock)
+register_part("block", "pre_norm_mixer_only", PreNormMixerOnlyBlock)
 register_part("block", "output_norm", OutputNormBlock)
 register_part("block", "output_norm_mixer_only", OutputNormMixerOnlyBlock)
 register_part("block", "parallel", ParallelBlock)

@@ -15,6 +15,13 @@ second batched product expands each head's weighted sum of latents with Uv_h.
 Rotation: interleaved pairs (2i, 2i+1) of the rotated part's first ``rot_dims`` numbers turn by
 position * ``rot_base``^(-2i / rot_dims); the rest passes unchanged.  Angles (float32 position times a
 float32 frequency rounded from float64), the latent's norm, scores and softmax are float32.
+
+Further parameters, for designs that differ:
+``q_rank``       the queries go through a latent of their own: c_q = RMS norm (weight ``dq.norm``) of W_dq x
+                 (``q_rank`` numbers), q = W_uq c_q (tensors ``dq``, ``dq.norm``, ``uq`` in the place of ``q``)
+``sink``         every head's softmax has one more key, of the learned score ``sink`` [heads], without a value
+``rot_scaling``  (``factor``, ``original``, ``fast``, ``slow``) the slow frequencies stretched and an amplitude on
+                 cos and sin, as ``rope_computed`` makes them
 """
 
 from __future__ import annotations
@@ -25,7 +32,8 @@ import torch
 
 from .. import ops
 from ..config.spec import PartSpec
-from .base import Mixer, PagedKVNeed, TensorDecl, register_part
+from ..config.spec import PartSpec as _PartSpec
+from .base import Mixer, PagedKVNeed, TensorDecl, build_part, register_part
 
 
 class LatentAttention(Mixer):
@@ -43,6 +51,9 @@ class LatentAttention(Mixer):
         self.rot_base = float(p.get("rot_base", 10000.0))
         self.rot_dims = int(p.get("rot_dims", self.r))
         self.eps = float(p["eps"])
+        self.q_rank = None if p.get("q_rank") is None else int(p["q_rank"])
+        self.sink = bool(p.get("sink", False))
+        self.rot_scaling = None if not p.get("rot_scaling") else dict(p["rot_scaling"])
         if self.rot_dims % 2 or not (0 <= self.rot_dims <= self.r):
             raise ValueError("latent_attention: rot_dims must be even and at most rot_dim")
         if self.R > 512:
@@ -50,11 +61,26 @@ class LatentAttention(Mixer):
         if self.window is not None and self.window <= 0:
             raise ValueError("latent_attention: the window must be positive")
         self.w_in = None
+        self.w_uq = self.q_norm_w = self.sink_w = None
+        self.amplitude = 1.0
 
     def tensors(self) -> Dict[str, TensorDecl]:
         h = self.hidden_size
+        d: Dict[str, TensorDecl] = {}
+        if self.q_rank is None:
+            d["q"] = TensorDecl((self.H * (self.d + self.r), h))
+        else:
+            d["dq"] = TensorDecl((self.q_rank, h))
+            d["dq.norm"] = TensorDecl((self.q_rank,), "norm")
+            d["uq"] = TensorDecl((self.H * (self.d + self.r), self.q_rank))
+        if self.sink:
+            d["sink"] = TensorDecl((self.H,), "bias", std=1.0)
+        d.update(self._kv_tensors())
+        return d
+
+    def _kv_tensors(self) -> Dict[str, TensorDecl]:
+        h = self.hidden_size
         return {
-            "q": TensorDecl((self.H * (self.d + self.r), h)),
             "dkv": TensorDecl((self.R + self.r, h)),
             "dkv.norm": TensorDecl((self.R,), "norm"),
             "uk": TensorDecl((self.H * self.d, self.R)),
@@ -63,7 +89,12 @@ class LatentAttention(Mixer):
         }
 
     def load(self, fetch, dtype, device) -> None:
-        q = fetch("q").to(dtype)
+        q = fetch("q" if self.q_rank is None else "dq").to(dtype)
+        if self.q_rank is not None:
+            self.w_uq = fetch("uq").to(dtype).to(device).contiguous()
+            self.q_norm_w = fetch("dq.norm").to(torch.float32).to(device).contiguous()
+        if self.sink:
+            self.sink_w = fetch("sink").to(torch.float32).to(device).contiguous()
         self.kv_off = (q.shape[0] + 7) // 8 * 8
         rows = [q]
         if self.kv_off != q.shape[0]:
@@ -74,13 +105,17 @@ class LatentAttention(Mixer):
         self.w_uk = fetch("uk").to(dtype).to(device).contiguous().view(self.H, self.d, self.R)
         self.w_uv_t = fetch("uv").to(dtype).to(device).contiguous().view(self.H, self.dv, self.R).transpose(1, 2)
         self.w_o = fetch("o").to(dtype).to(device).contiguous()
-        i = torch.arange(self.rot_dims // 2, dtype=torch.float64)
-        freq = self.rot_base ** (-2.0 * i / max(1, self.rot_dims))
+        # frequencies as the rotary part makes them (float64, the scaling's ramp, rounded once)
+        rope = build_part("position", _PartSpec("rope_computed", {
+            "rotary_dim": self.rot_dims, "theta": self.rot_base, "layout": "interleaved",
+            "scaling": self.rot_scaling if self.rot_dims else None}))
+        freq = rope.frequencies()
+        self.amplitude = float(rope.amplitude)
         self.freq = (freq.to(torch.float32) if freq.numel() else torch.zeros(1)).to(device).contiguous()
 
     def weight_bytes(self) -> int:
-        ts = [self.w_in, self.w_uk, self.w_uv_t, self.w_o]
-        return sum(t.numel() * t.element_size() for t in ts)
+        ts = [self.w_in, self.w_uk, self.w_uv_t, self.w_o, self.w_uq]
+        return sum(t.numel() * t.element_size() for t in ts if t is not None)
 
     def cache_need(self):
         return PagedKVNeed(1, self.R + self.r, self.window, value_head_dim=0)
@@ -100,11 +135,17 @@ class LatentAttention(Mixer):
     def forward(self, x, step, cache):
         n, dev, H, d, r, R = x.shape[0], x.device, self.H, self.d, self.r, self.R
         proj = ops.linear(x, self.w_in)
+        qrows = proj
+        if self.q_rank is not None:          # the queries' own latent: norm, then the second product
+            cq = torch.empty((n, self.q_rank), dtype=x.dtype, device=dev)
+            ops.rmsnorm(cq, proj[:, :self.q_rank], self.q_norm_w, self.eps)
+            qrows = ops.linear(cq, self.w_uq)
         q_full = torch.empty((n, H, R + r), dtype=x.dtype, device=dev)
         ops.latent_prepare(proj, 0, self.kv_off, self.norm_w, self.eps, self.freq, self.rot_dims, step.positions,
-                           cache.slot_map if cache.writable else None, cache.k, q_full, H, d, r, R, step.status)
+                           cache.slot_map if cache.writable else None, cache.k, q_full, H, d, r, R, step.status,
+                           amplitude=self.amplitude, q=qrows)
         # queries into the latent space: a_h = Uk_h^T q_h, written in front of the rotated parts
-        q_plain = proj[:, :H * (d + r)].view(n, H, d + r)[:, :, :d].permute(1, 0, 2)          # [H, n, d]
+        q_plain = qrows[:, :H * (d + r)].view(n, H, d + r)[:, :, :d].permute(1, 0, 2)         # [H, n, d]
         ops.batched_heads(q_plain, self.w_uk, out=q_full[:, :, :R].permute(1, 0, 2))            # [H, n, R]
         lat = torch.empty((n, H, R), dtype=x.dtype, device=dev)
         self.attend(lat, q_full, step, cache)
@@ -130,19 +171,21 @@ class LatentAttention(Mixer):
         entries = None if getattr(step, "captured", False) else getattr(step, "entries", None)
         if entries is None or all(len(e.tokens) < self.PRODUCT_MIN_TOKENS for e in entries):
             ops.latent_attention(lat, q_full, cache.k, cache.block_table, step, 0, n, *args,
-                                 *self._splits(n, step, lat.device))
+                                 *self._splits(n, step, lat.device), sink=self.sink_w)
             return
         t, run0 = 0, 0          # run0: first token of the current run of entries that go to the kernel
         for e, ctx in zip(entries, step.entry_ctx):
             q = len(e.tokens)
             if q >= self.PRODUCT_MIN_TOKENS:
                 if t > run0:
-                    ops.latent_attention(lat, q_full, cache.k, cache.block_table, step, run0, t - run0, *args)
+                    ops.latent_attention(lat, q_full, cache.k, cache.block_table, step, run0, t - run0, *args,
+                                         sink=self.sink_w)
                 self._attend_by_products(lat, q_full, cache, step, e.slot, t, q, ctx)
                 run0 = t + q
             t += q
         if n > run0:     # (padding entries of a captured step never come here: such a step has no host entries)
-            ops.latent_attention(lat, q_full, cache.k, cache.block_table, step, run0, n - run0, *args)
+            ops.latent_attention(lat, q_full, cache.k, cache.block_table, step, run0, n - run0, *args,
+                                 sink=self.sink_w)
 
     def _attend_by_products(self, lat, q_full, cache, step, slot, t0, count, ctx) -> None:
         """Tokens t0 .. t0 + count - 1 of the step: one request's positions ctx .. ctx + count - 1."""
@@ -160,7 +203,7 @@ class LatentAttention(Mixer):
             qb = q_full[t0 + b0:t0 + b0 + nb].view(nb * H, KD)
             scores = ops.linear(qb, keys, out_dtype=torch.float32)                       # [nb * H, keys]
             weights = torch.empty(scores.shape, dtype=lat.dtype, device=lat.device)
-            ops.latent_masked_softmax(weights, scores, H, p0, lo, self.window, self.scale)
+            ops.latent_masked_softmax(weights, scores, H, p0, lo, self.window, self.scale, sink=self.sink_w)
             ops.product(weights, keys[:, :R], out=lat[t0 + b0:t0 + b0 + nb].view(nb * H, R))
 
 

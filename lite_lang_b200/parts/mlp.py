@@ -73,7 +73,7 @@ class GatedMLP(FeedForward):
 
 class DenseMLP(FeedForward):
     """Feed-forward without a gate: down(act(up(x))), no biases; ``activation`` gelu_tanh (the tanh form of
-    GELU), relu or silu, evaluated in float32.  ``tensor_names``: (up, down) under the prefix."""
+    GELU), relu, silu or relu2 (the square of relu), evaluated in float32.  ``tensor_names``: (up, down) under the prefix."""
 
     def __init__(self, spec):
         super().__init__(spec)

@@ -16,8 +16,21 @@ One part, every mechanism a parameter, so that a design picks the ones it has:
 ``mask``, ``mask_size``  "causal"; "window": a token sees itself and the mask_size - 1 before it; "chunk": a
                       token sees the earlier tokens of its own chunk of mask_size positions, chunks counted
                       from the request's first token
-``sink``              the softmax's denominator gains a 1: one more key of score 0 that carries no value
+``sink``              the softmax's denominator gains a 1: one more key of score 0 that carries no value;
+                      "learned": the key's score is a number a head (tensor ``sink``), so the denominator gains
+                      exp(sink_h); the score is not scaled, capped or biased
 ``head_gate``         every head's output times sigmoid(w_h . x), x being the input of the projections
+``channel_gate``      every channel of every head's output times the sigmoid of its own gate input: the heads side
+                      by side times sigmoid(W_g x) (tensor ``g`` [heads * vdim, hidden])
+``distance_bias``     {"max": D}: a learned bias by distance, added to the scaled score: T[bucket(i - j), h] with
+                      the table ``rel`` [B, heads] (B is the tensor's), bucket(n) = n below B // 2, then
+                      logarithmic steps up to D, where the last bucket begins; {"buckets": B} only sizes random
+                      weights
+``keep_first``        with a window: the request's first ``keep_first`` positions stay visible to every later
+                      token (at their true distances); their pages stay with the request
+``softcap``           the scaled score goes through cap * tanh(s / cap) (before any bias)
+``query_temperature`` {"coef", "every"}: the query at position p is multiplied by
+                      1 + coef * ln(floor((p + 1) / every) + 1)
 
 The cache holds keys rotated and normalised and values normalised, one plane of pages; with a window or chunks
 the pages that no later token can read go back to the pool while the request lives.  Scores, softmax weights,
@@ -32,6 +45,7 @@ float32 arithmetic (``attention_modulated``).
 
 from __future__ import annotations
 
+import math
 from typing import Dict, Optional
 
 import torch
@@ -41,7 +55,17 @@ from ..config.spec import PartSpec
 from .base import Mixer, PagedKVNeed, TensorDecl, build_part, register_part
 
 _NAMES = {"q": "q", "k": "k", "v": "v", "o": "o", "q_bias": "q.b", "k_bias": "k.b", "v_bias": "v.b",
-          "q_norm": "q.norm", "k_norm": "k.norm", "temperature": "temp", "mix": "talk", "gate": "g"}
+          "q_norm": "q.norm", "k_norm": "k.norm", "temperature": "temp", "mix": "talk", "gate": "g",
+          "sink": "sink", "distance_bias": "rel"}
+
+
+def distance_bucket(n: int, buckets: int, farthest: float) -> int:
+    """The row of a distance-bias table for a key n positions back: one row a distance below buckets // 2, then
+    rows in logarithmic steps that reach the last row at ``farthest``."""
+    half = buckets // 2
+    if n < half:
+        return n
+    return min(buckets - 1, half + int(math.floor(math.log(n / half) / math.log(farthest / half) * (buckets - half))))
 
 
 class ModulatedAttention(Mixer):
@@ -61,7 +85,14 @@ class ModulatedAttention(Mixer):
         self.head_temperature = bool(p.get("head_temperature", False))
         self.head_mix = bool(p.get("head_mix", False))
         self.sink = bool(p.get("sink", False))
+        self.sink_learned = p.get("sink") == "learned"
         self.head_gate = bool(p.get("head_gate", False))
+        self.channel_gate = bool(p.get("channel_gate", False))
+        self.distance_bias = None if not p.get("distance_bias") else dict(p["distance_bias"])
+        self.keep_first = int(p.get("keep_first") or 0)
+        self.softcap = None if not p.get("softcap") else float(p["softcap"])
+        qt = p.get("query_temperature")
+        self.query_temperature = None if not qt else (float(qt["coef"]), int(qt["every"]))
         self.mask = str(p.get("mask", "causal"))
         size = p.get("mask_size")
         self.mask_size = None if size is None else int(size)
@@ -73,6 +104,16 @@ class ModulatedAttention(Mixer):
             raise ValueError(f"modulated_attention: mask {self.mask!r}; built: {', '.join(ops.ATTN_MASK)}")
         if self.mask != "causal" and (self.mask_size is None or self.mask_size <= 0):
             raise ValueError(f"modulated_attention: a {self.mask} mask needs a positive mask_size")
+        if self.head_gate and self.channel_gate:
+            raise ValueError("modulated_attention: a gate a head or a gate a channel, not both")
+        if self.keep_first and self.mask != "window":
+            raise ValueError("modulated_attention: keep_first goes with a window")
+        if self.distance_bias is not None and not float(self.distance_bias.get("max", 0)) > 1:
+            raise ValueError("modulated_attention: distance_bias needs 'max' (the distance of the last bucket) above 1")
+        if self.query_temperature is not None and self.query_temperature[1] <= 0:
+            raise ValueError("modulated_attention: query_temperature.every must be positive")
+        if self.head_mix and (self.distance_bias is not None or self.softcap is not None or self.sink_learned):
+            raise ValueError("modulated_attention: mixed heads with a distance bias, a cap or a learned sink are not built")
         pos = p.get("position")
         self.position = build_part("position", pos) if pos is not None else None
         if self.position is not None and not getattr(self.position, "computed", False):
@@ -87,6 +128,10 @@ class ModulatedAttention(Mixer):
         self.gate_offset = self.q_width + self.k_width + self.v_width
         self.w_in = self.b_in = self.w_o = None
         self.q_norm_w = self.k_norm_w = self.temperature = self.mix = None
+        self.sink_w = self.bias_by_distance = None
+        # mechanisms that only the block-a-token kernel and the extended tensor-core kernel know
+        self.extended = bool(self.sink_learned or self.channel_gate or self.distance_bias is not None
+                             or self.keep_first or self.softcap is not None or self.query_temperature is not None)
 
     def tensors(self) -> Dict[str, TensorDecl]:
         h, nm = self.hidden_size, self.names
@@ -105,11 +150,21 @@ class ModulatedAttention(Mixer):
             d[nm["mix"]] = TensorDecl((self.num_heads, self.num_heads), "bias", std=0.2, eye=1.0)
         if self.head_gate:
             d[nm["gate"]] = TensorDecl((self.num_heads, h))
+        if self.channel_gate:
+            d[nm["gate"]] = TensorDecl((self.o_width, h))
+        if self.sink_learned:
+            d[nm["sink"]] = TensorDecl((self.num_heads,), "bias", std=1.0)
+        if self.distance_bias is not None:
+            # the number of buckets is the tensor's; random weights take ``buckets`` (32 if the design gives none)
+            d[nm["distance_bias"]] = TensorDecl((None, self.num_heads), "bias", std=0.5,
+                                                random_shape=(int(self.distance_bias.get("buckets") or 32),
+                                                              self.num_heads))
         return d
 
     def load(self, fetch, dtype, device) -> None:
         nm = self.names
-        w = [fetch(nm[r]).to(dtype) for r in (("q", "k", "v", "gate") if self.head_gate else ("q", "k", "v"))]
+        gated = self.head_gate or self.channel_gate
+        w = [fetch(nm[r]).to(dtype) for r in (("q", "k", "v", "gate") if gated else ("q", "k", "v"))]
         rows = sum(t.shape[0] for t in w)
         if rows % 8:      # rows of the product start on 16-byte boundaries (the tensor-core attention reads q so)
             w.append(torch.zeros((8 - rows % 8, self.hidden_size), dtype=dtype, device=w[0].device))
@@ -128,6 +183,18 @@ class ModulatedAttention(Mixer):
             self.temperature = f32("temperature")
         if self.head_mix:
             self.mix = f32("mix")
+        if self.sink_learned:
+            self.sink_w = f32("sink")
+        if self.distance_bias is not None:
+            table = fetch(nm["distance_bias"]).to(torch.float32)
+            if table.dim() != 2 or table.shape[0] < 2:
+                raise ValueError(f"{self.prefix}{nm['distance_bias']}: a bias table needs at least two buckets")
+            far = float(self.distance_bias["max"])
+            if far <= table.shape[0] // 2:
+                raise ValueError(f"{self.prefix}: distance_bias.max must lie beyond the table's exact buckets")
+            # the bias a distance: from ceil(max) on every distance has the last bucket's
+            rows = [distance_bucket(n, table.shape[0], far) for n in range(int(math.ceil(far)) + 1)]
+            self.bias_by_distance = table[rows].to(device).contiguous()
 
     def weight_bytes(self) -> int:
         return self.w_in.numel() * self.w_in.element_size() + self.w_o.numel() * self.w_o.element_size()
@@ -136,7 +203,8 @@ class ModulatedAttention(Mixer):
         return PagedKVNeed(self.num_kv_heads, self.head_dim,
                            self.mask_size if self.mask == "window" else None,
                            None if self.vdim == self.head_dim else self.vdim,
-                           self.mask_size if self.mask == "chunk" else None)
+                           self.mask_size if self.mask == "chunk" else None,
+                           self.keep_first if self.mask == "window" else 0)
 
     def kernel_libraries(self):
         libs = ["core", "attn_mod"]
@@ -153,13 +221,27 @@ class ModulatedAttention(Mixer):
             self.position.prepare(device)
 
     # ------------------------------------------------------------------
+    # A composite mixer that joins its members in one output projection asks for the heads side by side, times a
+    # constant, written into its own buffer (``forward_inner``), and multiplies by ``inner_weight()`` itself.
+    @property
+    def inner_width(self) -> int:
+        return self.o_width
+
+    def inner_weight(self) -> torch.Tensor:
+        return self.w_o
+
     def forward(self, x, step, cache):
+        attn = torch.empty((x.shape[0], self.o_width), dtype=x.dtype, device=x.device)
+        self.forward_inner(x, step, cache, attn)
+        return ops.linear(attn, self.w_o, partial_ok=self.partial_ok)
+
+    def forward_inner(self, x, step, cache, attn, out_scale: float = 1.0) -> None:
         n = x.shape[0]
         proj = ops.linear(x, self.w_in)                  # q | k | v (| gate inputs)
         pos = self.position
         # bfloat16 with head sizes the tensor-core kernel takes: mixed heads become one wider query a head
-        shaped = ops.attn_shaped_supported(proj.dtype, self.num_kv_heads, self.head_dim, self.vdim, cache.page_size,
-                                           proj.stride(0), self.head_mix)
+        shaped = not self.extended and out_scale == 1.0 and ops.attn_shaped_supported(
+            proj.dtype, self.num_kv_heads, self.head_dim, self.vdim, cache.page_size, proj.stride(0), self.head_mix)
         mixed_q = None
         if shaped and self.head_mix:
             mixed_q = torch.empty((n, self.num_heads * self.num_kv_heads * self.head_dim), dtype=proj.dtype,
@@ -173,22 +255,26 @@ class ModulatedAttention(Mixer):
             self.eps, cache.slot_map if cache.writable else None, cache.k, cache.v, cache.page_size, step.status,
             head_mix=self.mix if mixed_q is not None else None,
             mix_temperature=self.temperature if (mixed_q is not None or fold) else None, mixed_q=mixed_q)
-        attn = torch.empty((n, self.o_width), dtype=x.dtype, device=x.device)
         if shaped:
             self.attend_shaped(attn, proj, mixed_q, step, cache, None if fold else self.temperature)
         else:
-            self.attend(attn, proj, step, cache)
-        return ops.linear(attn, self.w_o, partial_ok=self.partial_ok)
+            self.attend(attn, proj, step, cache, out_scale)
 
     def _gate(self, proj):
+        if self.channel_gate:
+            return proj[:, self.gate_offset:self.gate_offset + self.o_width]
         return proj[:, self.gate_offset:self.gate_offset + self.num_heads] if self.head_gate else None
 
-    def attend(self, out, proj, step, cache) -> None:
+    def attend(self, out, proj, step, cache, out_scale: float = 1.0) -> None:
         """Any sizes, both dtypes, float32 arithmetic: a block a token."""
         ops.attention_modulated(out, proj, proj.stride(0), self._gate(proj), cache.k, cache.v, cache.block_table,
                                 step.token_req, step.req_slot, step.positions, proj.shape[0], self.num_heads,
                                 self.num_kv_heads, self.head_dim, self.vdim, cache.page_size, self.mask,
-                                self.mask_size, self.sink, self.scale, self.temperature, self.mix, step.status)
+                                self.mask_size, self.sink, self.scale, self.temperature, self.mix, step.status,
+                                sink_values=self.sink_w, distance_bias=self.bias_by_distance,
+                                keep_first=self.keep_first, softcap=self.softcap,
+                                query_temperature=self.query_temperature, gate_channels=self.channel_gate,
+                                out_scale=out_scale)
 
     def attend_shaped(self, out, proj, mixed_q, step, cache, temperature) -> None:
         """Tensor cores.  Single-token entries come first in a step: their keys are cut into parts of one or more

@@ -3,7 +3,7 @@
 A router scores all ``experts`` in float32 (scores = ``score``(W_router x): "softmax" over all experts, or
 "sigmoid"), the ``top`` largest are chosen, and the output is the sum of the chosen experts' outputs weighted
 by their scores (divided by their sum first if ``renormalize``).  An expert is down(act(up x)) without biases,
-act = ``activation`` ("relu2": the square of relu; "silu"; "gelu_tanh").  ``shared_ff`` > 0 adds an expert of
+act = ``activation`` ("relu2": the square of relu; "silu"; "gelu_tanh"; "gelu": the erf form).  ``shared_ff`` > 0 adds an expert of
 that width (tensors ``shared.up``, ``shared.down``) that runs for every token with weight 1.
 
 Two ways through the experts, both without the host ever knowing who chose whom:
@@ -27,6 +27,9 @@ Further parameters, for designs that differ:
 ``score``         "softmax_top": the ``top`` largest logits are chosen, weighted by the softmax over the chosen only.
 ``router_bias``   a bias on the router's logits (tensor ``router.b``).
 ``shared_gate``   the shared expert's output is multiplied by sigmoid(w . x), one number a token (``shared.sg``).
+``weight_on``     "output" (the sum of w_e expert_e(x)) or "input": the sum of expert_e(w_e x), the weight
+                  multiplying what the expert reads.  Since U (w x) = w (U x) the first product is the same and
+                  the weight goes inside the activation: down(act(w (up x))).
 """
 
 from __future__ import annotations
@@ -57,6 +60,10 @@ class RoutedExperts(FeedForward):
         self.swish_alpha = float(p.get("swish_alpha", 1.702))
         self.router_bias = bool(p.get("router_bias", False))
         self.shared_gate = bool(p.get("shared_gate", False)) and self.shared_ff > 0
+        self.weight_on = str(p.get("weight_on", "output"))
+        if self.weight_on not in ("output", "input") or (self.gated and self.weight_on == "input"):
+            raise ValueError("routed_experts: weight_on is 'output' or (experts without a gate) 'input'")
+        self.weight_in = self.weight_on == "input"
         if self.gated and not (self.limit > 0 and self.shared_limit > 0):
             raise ValueError("routed_experts: gated experts take a positive limit")
         if (not self.gated and self.activation not in ops.MOE_ACT) or self.score not in ops.MOE_SCORE:
@@ -147,7 +154,7 @@ class RoutedExperts(FeedForward):
             hidden = ops.moe_gated_act(hidden, gates, self._shared_w, self.shared_ff, self.ff, self.E, self.limit,
                                        self.shared_limit, self.swish_alpha)
         else:
-            ops.moe_act(hidden, gates, self.shared_ff, self.ff, self.E, self.activation)
+            ops.moe_act(hidden, gates, self.shared_ff, self.ff, self.E, self.activation, self.weight_in)
         # (few tokens and many hidden units: float32 partial sums of a split inner dimension, added up by the norm)
         return ops.linear(hidden, self.w_down, partial_ok=True)
 
@@ -169,7 +176,7 @@ class RoutedExperts(FeedForward):
         if self.gated:
             hidden = ops.moe_row_gated_act(hidden, row_w, self.limit, self.swish_alpha)
         else:
-            ops.moe_row_act(hidden, row_w, self.activation)
+            ops.moe_row_act(hidden, row_w, self.activation, self.weight_in)
         y = ops.grouped_product(hidden, self.w_down_experts, ends)
         return ops.moe_combine(base, y, pair_row)
 

@@ -35,7 +35,8 @@ def main(argv=None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True, dest="max_tokens")
     ap.add_argument("--page-size", type=int, default=16, dest="page_size",
                     help="tokens per cache page (default 16; must divide 64 or be a multiple of it)")
-    ap.add_argument("--max-requests", type=int, default=8, dest="max_requests")
+    ap.add_argument("--max-requests", type=int, default=4, dest="max_requests",
+                    help="request slots (block-table rows and state records); at most this many requests are live")
     ap.add_argument("--no-cuda-graphs", action="store_true", dest="no_graphs")
     args = ap.parse_args(argv)
 

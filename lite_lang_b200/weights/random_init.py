@@ -26,6 +26,8 @@ def draw_tensor(name: str, decl, seed: int, scales: Mapping[str, float], dtype: 
     gen = torch.Generator(device=device)
     gen.manual_seed((int(seed) * 1000003 + zlib.crc32(name.encode())) % (2 ** 63))
     shape = tuple(decl.shape)
+    if any(n is None for n in shape) and getattr(decl, "random_shape", None) is not None:
+        shape = tuple(decl.random_shape)
     if any(n is None for n in shape):
         raise ValueError(f"tensor {name}: a size that only a checkpoint gives; name it in the configuration "
                          "to draw random weights")
