@@ -509,7 +509,33 @@ def _lenuzen_shape(width, heads, kv_heads, head, inter, vocab, layers, window, e
                         "mlp": {"kind": "dense", "ff": 3 * inter // 2 // 64 * 64}} for i in range(layers)]}
 
 
-COMPARE_DESIGNS = {"nevurax": _nevurax_shape, "redirax": _redirax_shape, "lenuzen": _lenuzen_shape}
+def _rufisun_shape(width, heads, kv_heads, head, inter, vocab, layers, window, experts, top):
+    """A Rufisun model whose layers are as large as a Qwen2 layer of the given sizes.  The layers take turns: the
+    windowed attention with a distance bias, 64 kept first tokens, a sink and a gate a channel (same heads, values as
+    wide as keys); the latent attention (a latent of four key heads, queries through a latent of 3/4 of the width);
+    the attention with capped scores beside a state-space layer of as many heads (state of 128, one group).  The
+    first layer's feed-forward is the dense one without a gate (two matrices of 1.5 x inter hidden units), the
+    others route ``top`` of ``experts`` experts (+ a shared one) with as many *active* weights."""
+    ff = (3 * inter // 2) // (top + 1) // 64 * 64
+    moe = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff}, "shared": {"ff": ff}}
+    dense = {"kind": "dense", "ff": 3 * inter // 2 // 64 * 64}
+    attention = {"heads": heads, "kv_heads": kv_heads, "dim": head, "vdim": head, "scale": head ** -0.5,
+                 "bias_max": 4 * window, "mask": {"size": window, "keep_first": 64}}
+    latent = {"heads": heads, "dim": head - 32, "rot_dim": 32, "vdim": head, "kv_rank": 4 * head,
+              "q_rank": 3 * width // 4 // 64 * 64, "scale": head ** -0.5,
+              "rot": {"base": 1e6, "dims": 32, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    parallel = {"left": {"heads": heads, "kv_heads": kv_heads, "dim": head, "vdim": head, "scale": head ** -0.5,
+                         "q_temp": {"coef": 0.1, "every": 1024}, "softcap": 30.0},
+                "right": {"heads": heads, "vdim": head, "state": 128, "groups": 1, "conv": 4, "norm_groups": 1},
+                "left_scale": 1.0, "right_scale": 1.0}
+    kinds = [("attention", attention), ("latent_attention", latent), ("parallel", parallel), ("attention", attention)]
+    return {"architecture": "Rufisun", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+            "layers": [{"type": kinds[i % 4][0], "mixer": kinds[i % 4][1], "mlp": dense if i % 4 == 0 else moe}
+                       for i in range(layers)]}
+
+
+COMPARE_DESIGNS = {"nevurax": _nevurax_shape, "redirax": _redirax_shape, "lenuzen": _lenuzen_shape,
+                   "rufisun": _rufisun_shape}
 
 COMPARE_SIZES = {
     # name: (Qwen2 sizes, window of the latent attention, experts, top)
@@ -560,6 +586,11 @@ def run_compare(args):
             qwen["hidden_size"] // qwen["num_attention_heads"], qwen["intermediate_size"], qwen["vocab_size"], layers,
             window, experts, top)
         designs = (("qwen2", qwen), (design_name, nev))
+        if args.against and args.against != "qwen2":      # another design of this package as the arm beside it
+            designs = ((args.against, COMPARE_DESIGNS[args.against](
+                qwen["hidden_size"], qwen["num_attention_heads"], qwen["num_key_value_heads"],
+                qwen["hidden_size"] // qwen["num_attention_heads"], qwen["intermediate_size"], qwen["vocab_size"],
+                layers, window, experts, top)), designs[1])
         if args.design_only:
             designs = designs[1:]
         for design, model in designs:
@@ -599,7 +630,10 @@ def run_compare(args):
             row[design] = r
             del engine
             torch.cuda.empty_cache()
-        if design_name == "lenuzen":
+        if design_name == "rufisun":
+            row["config"] = {design_name: {"window": window, "keep_first": 64, "experts": experts, "top": top,
+                                           "expert_ff": nev["layers"][-1]["mlp"]["expert"]["ff"] if layers > 1 else None}}
+        elif design_name == "lenuzen":
             row["config"] = {design_name: {"window": window, "chunk": window, "ff": nev["layers"][-1]["mlp"]["ff"]}}
         else:
             row["config"] = {design_name: {"window": window if design_name == "nevurax" else None, "experts": experts,
@@ -713,7 +747,9 @@ def main():
                     help="with --only: the layer sizes of that workload's model instead of Qwen2-1.5B's")
     ap.add_argument("--design-only", action="store_true", dest="design_only",
                     help="with --compare: leave the Qwen2 arm out")
-    ap.add_argument("--compare", default="", choices=["", "nevurax", "redirax", "lenuzen"],
+    ap.add_argument("--against", default="", choices=["", "qwen2", "nevurax", "redirax", "lenuzen"],
+                    help="with --compare: the arm beside the design (default qwen2)")
+    ap.add_argument("--compare", default="", choices=["", "nevurax", "redirax", "lenuzen", "rufisun"],
                     help="instead of the headline measurement: prefill and decode of a few layers of that design beside "
                          "Qwen2 at equal layer sizes (random weights); --layers (default 4), --size, --kernels go with it")
     ap.add_argument("--size", default="", dest="shape_name", choices=[""] + sorted(COMPARE_SIZES),

@@ -23,6 +23,12 @@
 // terms (P = hi + lo, sixteen bits of mantissa) accumulated in float32, so that they are not rounded to
 // eight bits where the design wants them in 32-bit.
 // Head sizes 64 and 128 (keys and values separately), page sizes that are multiples of 16.
+//
+// Further shapes of the scores, as in attention_modulated.cu: a factor on the query that grows with its position
+// (1 + coef ln(floor((p + 1) / every) + 1)); a cap, s <- cap tanh(s / cap); a bias by distance from a table
+// [distances, heads], added after the cap; with a window, the request's first `keep` positions stay visible (the
+// stages that hold them are walked before the window's: by part 0 where the keys are split); a sink of a learned
+// score a head in the place of 0; a sigmoid gate a channel in the place of one a head; a constant on the output.
 #include "common.cuh"
 
 #define AS_WARPS 8
@@ -53,7 +59,23 @@ struct AttnShapedParams {
   int* status;
   int nsplit, span;     // nsplit > 1: every entry brings one token; CTA z takes stages [first + z span, + span)
   float* part;          // [tokens, nh, nsplit, VD + 2]: sums, then the maximum (log2 domain) and the sum
+  const float* sink_val;  // optional [nh]: the sink's score (natural units) in the place of 0
+  const float* rel;       // optional [nd, nh]: bias of a key min(n, nd - 1) positions back (natural units)
+  int nd;
+  int keep;               // with mask 1: positions below it stay visible
+  float cap_log2, inv_cap_log2;   // cap > 0: scores through cap tanh(s / cap); here cap log2(e) and its inverse
+  float qt_coef;
+  int qt_every;           // > 0: the query's factor by position
+  int gate_channels;      // the gate is a number a channel: token t, head h, channel d at gate[t * gate_stride + h * VD + d]
+  float out_scale;
 };
+#define AS_LOG2E 1.4426950408889634f
+// tanh from exp2 and a division: absolute error of a few 1e-7
+__device__ __forceinline__ float as_tanh(float x) {
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * 2.885390081777927f));
+  return 1.0f - __fdividef(2.0f, e + 1.0f);
+}
 
 __device__ __forceinline__ void as_mma(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
                                        unsigned b1) {
@@ -165,7 +187,9 @@ __global__ void __launch_bounds__(AS_THREADS) attn_shaped_kernel(const AttnShape
     posr[i] = ctx + tokr[i];
     lor[i] = as_first_visible(p.mask, p.mask_size, posr[i]);
     sc[i] = p.scale_log2 * ((!MIX && p.temp) ? p.temp[headr[i]] : 1.0f);
+    if (p.qt_every > 0) sc[i] *= 1.0f + p.qt_coef * logf((float)((posr[i] + 1) / p.qt_every) + 1.0f);
   }
+  const int keep = p.mask == 1 ? p.keep : 0;
   // key ranges: of the CTA (what is loaded) and of the warp (what it computes on); the first visible key
   // never decreases with the position, so the first row has the smallest and the last row the largest one
   const int cta_last_row = min(total_rows, r0 + AS_ROWS) - 1;
@@ -180,6 +204,9 @@ __global__ void __launch_bounds__(AS_THREADS) attn_shaped_kernel(const AttnShape
 
   const int* bt = p.block_table + (size_t)slot * p.bt_stride;
   int T_first = cta_lo / AS_TK, T_last = cta_hi / AS_TK;
+  // the stages that hold kept first positions and lie before the window's first stage are walked first
+  int nkeep = keep > 0 ? min((keep - 1) / AS_TK + 1, T_first) : 0;
+  if (split && z != 0) nkeep = 0;
   if (split) {
     T_first += z * p.span;
     if (T_first > T_last) return;      // the second kernel counts the parts of a row from its position
@@ -196,7 +223,7 @@ __global__ void __launch_bounds__(AS_THREADS) attn_shaped_kernel(const AttnShape
       const int pos = T * AS_TK + key;
       const bf16* ksrc = p.k_cache;
       int bytes = 0;
-      if (pos <= cta_hi && pos >= cta_lo) {
+      if (pos <= cta_hi && (pos >= cta_lo || pos < keep)) {
         const int page = bt[pos / p.page_size];
         if (page >= 0 && page < p.num_pages) {
           ksrc += (((size_t)page * p.nkv + (MIX ? kl : kvh)) * p.page_size + (pos % p.page_size)) * HD + 8 * chunk;
@@ -215,7 +242,7 @@ __global__ void __launch_bounds__(AS_THREADS) attn_shaped_kernel(const AttnShape
       const int pos = T * AS_TK + key;
       const bf16* vsrc = p.v_cache;
       int bytes = 0;
-      if (pos <= cta_hi && pos >= cta_lo) {
+      if (pos <= cta_hi && (pos >= cta_lo || pos < keep)) {
         const int page = bt[pos / p.page_size];
         if (page >= 0 && page < p.num_pages) {
           vsrc += (((size_t)page * p.nkv + kvh) * p.page_size + (pos % p.page_size)) * VD + 8 * chunk;
@@ -231,15 +258,22 @@ __global__ void __launch_bounds__(AS_THREADS) attn_shaped_kernel(const AttnShape
   for (int t = 0; t < NT; ++t) o_acc[t][0] = o_acc[t][1] = o_acc[t][2] = o_acc[t][3] = 0.f;
   // the sink is a key of score 0 that every row sees (with splits the second kernel adds it)
   const bool sink_here = p.sink && !split;
-  float m_run[2], l_run[2];
-  m_run[0] = m_run[1] = sink_here ? 0.f : -INFINITY;
-  l_run[0] = l_run[1] = 0.f;   // (a thread holds a quarter of a row's sum: the sink's 1 is added after the reduction)
+  float m_run[2], l_run[2], sink_log2[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    sink_log2[i] = p.sink_val ? p.sink_val[headr[i]] * AS_LOG2E : 0.f;
+    m_run[i] = sink_here ? sink_log2[i] : -INFINITY;
+    l_run[i] = 0.f;   // (a thread holds a quarter of a row's sum: the sink's term is added after the reduction)
+  }
+  const int n_stages = nkeep + (T_last - T_first + 1);
+  auto stage_T = [&](int n) { return n < nkeep ? n : T_first + (n - nkeep); };
 
-  load_stage(0, T_first);
+  load_stage(0, stage_T(0));
   as_commit();
-  for (int T = T_first; T <= T_last; ++T) {
-    const int buf = (T - T_first) & 1;
-    if (T < T_last) load_stage(buf ^ 1, T + 1);
+  for (int n = 0; n < n_stages; ++n) {
+    const int T = stage_T(n);
+    const int buf = n & 1;
+    if (n + 1 < n_stages) load_stage(buf ^ 1, stage_T(n + 1));
     as_commit();
     as_wait<1>();      // everything but the newest group has landed: stage T is complete
     __syncthreads();
@@ -247,7 +281,7 @@ __global__ void __launch_bounds__(AS_THREADS) attn_shaped_kernel(const AttnShape
 #pragma unroll 1
       for (int sub = 0; sub < AS_TK / 32; ++sub) {
         const int key0 = T * AS_TK + 32 * sub;
-        if (key0 > w_hi || key0 + 31 < w_lo) continue;  // nothing of this piece is visible to the warp's rows
+        if (key0 > w_hi || (key0 + 31 < w_lo && key0 >= keep)) continue;  // nothing of this piece is visible to the warp's rows
         const unsigned kt = k_base + buf * kt_bytes + (32 * sub) * kpitch;
         const unsigned vt = v_base + buf * VT_BYTES + (32 * sub) * VROW;
         // ---- S = Q K^T for 32 keys: four column tiles, two accumulation chains each ----
@@ -295,9 +329,11 @@ __global__ void __launch_bounds__(AS_THREADS) attn_shaped_kernel(const AttnShape
           for (int x = 0; x < 4; ++x) {
             const int i = x >> 1;
             float v = (s_acc[u][x] + s_odd[u][x]) * sc[i];
-            if (boundary) {
+            if (p.cap_log2 > 0.f) v = p.cap_log2 * as_tanh(v * p.inv_cap_log2);
+            if (boundary || p.rel) {
               const int j = key0 + 8 * u + 2 * c + (x & 1);
-              if (j > posr[i] || j < lor[i]) v = -INFINITY;
+              if (p.rel) v = fmaf(p.rel[(size_t)min(max(posr[i] - j, 0), p.nd - 1) * p.nh + headr[i]], AS_LOG2E, v);
+              if (j > posr[i] || (j < lor[i] && j >= keep)) v = -INFINITY;
             }
             s_acc[u][x] = v;
             tmax[i] = fmaxf(tmax[i], v);
@@ -411,9 +447,9 @@ __global__ void __launch_bounds__(AS_THREADS) attn_shaped_kernel(const AttnShape
   float inv[2];
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
-    const float l = l_run[i] + (sink_here ? as_exp2(-m_run[i]) : 0.f);
-    inv[i] = l > 0.f ? 1.0f / l : 0.f;
-    if (p.gate) {
+    const float l = l_run[i] + (sink_here ? as_exp2(sink_log2[i] - m_run[i]) : 0.f);
+    inv[i] = (l > 0.f ? 1.0f / l : 0.f) * p.out_scale;
+    if (p.gate && !p.gate_channels) {
       const float gv = __bfloat162float(p.gate[(size_t)(tok0 + tokr[i]) * p.gate_stride + headr[i]]);
       inv[i] *= 1.0f / (1.0f + expf(-gv));
     }
@@ -425,10 +461,19 @@ __global__ void __launch_bounds__(AS_THREADS) attn_shaped_kernel(const AttnShape
   for (int Tn = 0; Tn < NT; ++Tn) {
     const int h = Tn >> 3, j = Tn & 7;
     const int d0 = 64 * h + 16 * c + j, d1 = d0 + 8;
-    stage[g * (VD + 8) + d0] = __float2bfloat16_rn(o_acc[Tn][0] * inv[0]);
-    stage[g * (VD + 8) + d1] = __float2bfloat16_rn(o_acc[Tn][1] * inv[0]);
-    stage[(g + 8) * (VD + 8) + d0] = __float2bfloat16_rn(o_acc[Tn][2] * inv[1]);
-    stage[(g + 8) * (VD + 8) + d1] = __float2bfloat16_rn(o_acc[Tn][3] * inv[1]);
+    float ga[2] = {1.f, 1.f}, gb[2] = {1.f, 1.f};      // a gate a channel: before the value's one rounding
+    if (p.gate && p.gate_channels) {
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const bf16* gr = p.gate + (size_t)(tok0 + tokr[i]) * p.gate_stride + (size_t)headr[i] * VD;
+        ga[i] = 1.0f / (1.0f + expf(-__bfloat162float(gr[d0])));
+        gb[i] = 1.0f / (1.0f + expf(-__bfloat162float(gr[d1])));
+      }
+    }
+    stage[g * (VD + 8) + d0] = __float2bfloat16_rn(o_acc[Tn][0] * inv[0] * ga[0]);
+    stage[g * (VD + 8) + d1] = __float2bfloat16_rn(o_acc[Tn][1] * inv[0] * gb[0]);
+    stage[(g + 8) * (VD + 8) + d0] = __float2bfloat16_rn(o_acc[Tn][2] * inv[1] * ga[1]);
+    stage[(g + 8) * (VD + 8) + d1] = __float2bfloat16_rn(o_acc[Tn][3] * inv[1] * gb[1]);
   }
   __syncwarp();
   for (int idx = lane; idx < 16 * VCPR; idx += 32) {
@@ -461,9 +506,10 @@ __global__ void __launch_bounds__(VD) attn_shaped_join_kernel(const AttnShapedPa
   const int stages = pos / AS_TK - as_first_visible(p.mask, p.mask_size, pos) / AS_TK + 1;
   const int parts = min(p.nsplit, (stages + p.span - 1) / p.span);
   const float* src = p.part + ((size_t)tok * p.nh + head) * p.nsplit * (VD + 2);
-  float M = p.sink ? 0.f : -INFINITY;
+  const float sink_log2 = p.sink_val ? p.sink_val[head] * AS_LOG2E : 0.f;
+  float M = p.sink ? sink_log2 : -INFINITY;
   for (int zz = 0; zz < parts; ++zz) M = fmaxf(M, src[(size_t)zz * (VD + 2) + VD]);
-  float L = (p.sink && M > -INFINITY) ? as_exp2(-M) : 0.f, acc = 0.f;
+  float L = (p.sink && M > -INFINITY) ? as_exp2(sink_log2 - M) : 0.f, acc = 0.f;
   for (int zz = 0; zz < parts; ++zz) {
     const float* s = src + (size_t)zz * (VD + 2);
     const float m = s[VD];
@@ -471,8 +517,10 @@ __global__ void __launch_bounds__(VD) attn_shaped_join_kernel(const AttnShapedPa
     L = fmaf(s[VD + 1], w, L);
     acc = fmaf(s[d], w, acc);
   }
-  float r = L > 0.f ? acc / L : 0.f;
-  if (p.gate) r *= 1.0f / (1.0f + expf(-__bfloat162float(p.gate[(size_t)tok * p.gate_stride + head])));
+  float r = (L > 0.f ? acc / L : 0.f) * p.out_scale;
+  if (p.gate)
+    r *= 1.0f / (1.0f + expf(-__bfloat162float(p.gate[(size_t)tok * p.gate_stride +
+                                                       (p.gate_channels ? (size_t)head * VD + d : (size_t)head)])));
   o[d] = __float2bfloat16_rn(r);
 }
 
@@ -488,6 +536,8 @@ extern "C" long ll_attn_shaped_smem(int nkv, int hd, int vd, int mixed) {
 // gate[t * gate_stride + h]; temp (optional, ignored with `mixed`: it is inside Q'): float32 [nh].
 // out [tokens, nh * vd].  k_cache [pages, nkv, page_size, hd], v_cache [pages, nkv, page_size, vd].
 // cu_q, ctx_len, req_slot: the entries; row_blocks = sum over them of ceil(q_len * group / 128).
+// sink_val (optional float32 [nh]), rel (optional float32 [nd, nh]), keep, cap (0: none), qt_coef / qt_every
+// (0: none), gate_channels, out_scale: see the head of this file.
 // mask 0 causal, 1 window, 2 chunks of mask_size.  nsplit > 1 (every entry brings one token): the keys of a
 // row are cut into parts of `span` stages of 64 keys; part float32 [tokens, nh, nsplit, vd + 2].
 extern "C" int ll_attn_shaped(void* out, long out_stride, const void* q, long q_stride, int mixed, const void* gate,
@@ -495,13 +545,17 @@ extern "C" int ll_attn_shaped(void* out, long out_stride, const void* q, long q_
                               const int* block_table, int bt_stride, const int* cu_q, const int* ctx_len,
                               const int* req_slot, int n_entries, int row_blocks, int nh, int nkv, int hd, int vd,
                               int page_size, int num_pages, int mask, int mask_size, int sink, float scale, int nsplit,
-                              int span, float* part, int* status, cudaStream_t stream) {
+                              int span, float* part, int* status, const float* sink_val, const float* rel, int nd,
+                              int keep, float cap, float qt_coef, int qt_every, int gate_channels, float out_scale,
+                              cudaStream_t stream) {
   if (row_blocks <= 0 || n_entries <= 0) return 0;
   const long smem = ll_attn_shaped_smem(nkv, hd, vd, mixed);
   if (smem == 0 || page_size % 16 != 0 || nh % nkv != 0 || nkv > 65535 || mask < 0 || mask > 2 ||
       (mask != 0 && mask_size <= 0) || nsplit < 1 || nsplit > 65535 || (nsplit > 1 && (part == nullptr || span < 1)))
     return (int)cudaErrorInvalidValue;
-  if ((q_stride % 8) != 0 || (out_stride % 8) != 0) return (int)cudaErrorInvalidValue;
+  if ((q_stride % 8) != 0 || (out_stride % 8) != 0 || (rel != nullptr && nd <= 0) || keep < 0 ||
+      (mixed && (rel != nullptr || cap > 0.f || sink_val != nullptr)))
+    return (int)cudaErrorInvalidValue;
   AttnShapedParams p;
   p.q = (const bf16*)q;
   p.q_stride = q_stride;
@@ -531,6 +585,16 @@ extern "C" int ll_attn_shaped(void* out, long out_stride, const void* q, long q_
   p.nsplit = nsplit;
   p.span = span;
   p.part = part;
+  p.sink_val = sink ? sink_val : nullptr;
+  p.rel = rel;
+  p.nd = nd;
+  p.keep = keep;
+  p.cap_log2 = cap > 0.f ? cap * AS_LOG2E : 0.f;
+  p.inv_cap_log2 = cap > 0.f ? 1.0f / (cap * AS_LOG2E) : 0.f;
+  p.qt_coef = qt_coef;
+  p.qt_every = qt_every;
+  p.gate_channels = gate_channels;
+  p.out_scale = out_scale;
   dim3 grid(row_blocks, nkv, nsplit);
 #define AS_LAUNCH(HD_, VD_, MIX_)                                                                                  \
   do {                                                                                                             \

@@ -1739,14 +1739,27 @@ def attn_shaped(out: torch.Tensor, q: torch.Tensor, q_stride: int, mixed: bool, 
                 block_table: torch.Tensor, cu_q: torch.Tensor, ctx_len: torch.Tensor, req_slot: torch.Tensor,
                 num_entries: int, row_blocks: int, num_heads: int, num_kv_heads: int, head_dim: int,
                 value_head_dim: int, page_size: int, mask: str, mask_size: Optional[int], sink: bool, scale: float,
-                status: Optional[torch.Tensor], nsplit: int = 1, span: int = 1) -> None:
+                status: Optional[torch.Tensor], nsplit: int = 1, span: int = 1,
+                sink_values: Optional[torch.Tensor] = None, distance_bias: Optional[torch.Tensor] = None,
+                keep_first: int = 0, softcap: Optional[float] = None,
+                query_temperature: Optional[Tuple[float, int]] = None, gate_channels: bool = False,
+                out_scale: float = 1.0) -> None:
     """Tensor-core paged attention (bfloat16) with shaped scores: the mechanisms of ``attention_modulated`` for
     head sizes 64 and 128.  ``q``: the projection's rows (head h at h * head_dim), or with ``mixed`` the wider
     queries that ``qkv_norm_rotate_store`` leaves for mixed heads (then ``temperature`` is inside them).
     ``nsplit`` > 1 (every entry brings one token): the keys of a row are cut into parts of ``span`` stages of 64
-    keys, each a CTA, joined by a second kernel; nsplit * span must cover the stages any token sees.  Launches one
-    kernel, two with ``nsplit`` > 1."""
-    _need_cuda(out, q, gate, temperature, k_cache, v_cache, block_table, cu_q, ctx_len, req_slot)
+    keys, each a CTA, joined by a second kernel; nsplit * span must cover the stages any token sees (kept first
+    tokens' stages before the window's are walked by the first part besides).  ``sink_values``, ``distance_bias``,
+    ``keep_first``, ``softcap``, ``query_temperature``, ``gate_channels`` and ``out_scale`` are those of
+    ``attention_modulated``.  Launches one kernel, two with ``nsplit`` > 1."""
+    _need_cuda(out, q, gate, temperature, k_cache, v_cache, block_table, cu_q, ctx_len, req_slot, sink_values,
+               distance_bias)
+    _f32(sink_values, "sink_values")
+    _f32(distance_bias, "distance_bias")
+    _need(sink_values is None or (sink and sink_values.numel() == num_heads), "sink_values: a number a head")
+    _need(distance_bias is None or (distance_bias.dim() == 2 and distance_bias.shape[1] == num_heads
+                                    and distance_bias.is_contiguous()), "distance_bias is [distances, heads]")
+    qt_coef, qt_every = (0.0, 0) if query_temperature is None else (float(query_temperature[0]), int(query_temperature[1]))
     for t, nm in ((block_table, "block_table"), (cu_q, "cu_q"), (ctx_len, "ctx_len"), (req_slot, "req_slot")):
         _i32(t, nm)
     _f32(temperature, "temperature")
@@ -1762,7 +1775,9 @@ def attn_shaped(out: torch.Tensor, q: torch.Tensor, q_stride: int, mixed: bool, 
     _need(cu_q.numel() >= num_entries + 1 and ctx_len.numel() >= num_entries and req_slot.numel() >= num_entries,
           "attn_shaped: entry arrays too short")
     _need(temperature is None or temperature.numel() == num_heads, "temperature: a number a head")
-    _need(gate is None or (gate.dtype == q.dtype and gate.stride(1) == 1), "gate: [tokens, heads] rows")
+    _need(gate is None or (gate.dtype == q.dtype and gate.stride(1) == 1
+                           and gate.shape[1] == (num_heads * value_head_dim if gate_channels else num_heads)),
+          "gate: [tokens, heads] rows (or a number a channel)")
     _need(mask == "causal" or (mask_size or 0) > 0, "a window or chunks need a size")
     part = None
     if nsplit > 1:
@@ -1775,7 +1790,10 @@ def attn_shaped(out: torch.Tensor, q: torch.Tensor, q_stride: int, mixed: bool, 
         c_int(num_entries), c_int(row_blocks), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim),
         c_int(value_head_dim), c_int(page_size), c_int(k_cache.shape[0]), c_int(ATTN_MASK[mask]),
         c_int(int(mask_size or 0)), c_int(1 if sink else 0), c_float(scale), c_int(nsplit), c_int(span), _ptr(part),
-        _ptr(status), _stream())
+        _ptr(status), _ptr(sink_values), _ptr(distance_bias),
+        c_int(0 if distance_bias is None else distance_bias.shape[0]), c_int(int(keep_first or 0)),
+        c_float(float(softcap or 0.0)), c_float(qt_coef), c_int(qt_every), c_int(1 if gate_channels else 0),
+        c_float(out_scale), _stream())
 
 
 def attention_modulated(out: torch.Tensor, q: torch.Tensor, q_stride: int, gate: Optional[torch.Tensor],

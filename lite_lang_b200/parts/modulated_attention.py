@@ -24,8 +24,8 @@ One part, every mechanism a parameter, so that a design picks the ones it has:
                       by side times sigmoid(W_g x) (tensor ``g`` [heads * vdim, hidden])
 ``distance_bias``     {"max": D}: a learned bias by distance, added to the scaled score: T[bucket(i - j), h] with
                       the table ``rel`` [B, heads] (B is the tensor's), bucket(n) = n below B // 2, then
-                      logarithmic steps up to D, where the last bucket begins; {"buckets": B} only sizes random
-                      weights
+                      B // 2 + floor(ln(n / (B // 2)) / ln(D / (B // 2)) * (B - B // 2)), capped at the last row
+                      (which D has reached); {"buckets": B} only sizes random weights
 ``keep_first``        with a window: the request's first ``keep_first`` positions stay visible to every later
                       token (at their true distances); their pages stay with the request
 ``softcap``           the scaled score goes through cap * tanh(s / cap) (before any bias)
@@ -61,7 +61,7 @@ _NAMES = {"q": "q", "k": "k", "v": "v", "o": "o", "q_bias": "q.b", "k_bias": "k.
 
 def distance_bucket(n: int, buckets: int, farthest: float) -> int:
     """The row of a distance-bias table for a key n positions back: one row a distance below buckets // 2, then
-    rows in logarithmic steps that reach the last row at ``farthest``."""
+    rows in logarithmic steps, capped at the last row (which ``farthest`` has reached)."""
     half = buckets // 2
     if n < half:
         return n
@@ -129,7 +129,7 @@ class ModulatedAttention(Mixer):
         self.w_in = self.b_in = self.w_o = None
         self.q_norm_w = self.k_norm_w = self.temperature = self.mix = None
         self.sink_w = self.bias_by_distance = None
-        # mechanisms that only the block-a-token kernel and the extended tensor-core kernel know
+        # mechanisms that the block-a-token kernel and the mma.sync kernel know and the tcgen05 kernel does not
         self.extended = bool(self.sink_learned or self.channel_gate or self.distance_bias is not None
                              or self.keep_first or self.softcap is not None or self.query_temperature is not None)
 
@@ -240,7 +240,7 @@ class ModulatedAttention(Mixer):
         proj = ops.linear(x, self.w_in)                  # q | k | v (| gate inputs)
         pos = self.position
         # bfloat16 with head sizes the tensor-core kernel takes: mixed heads become one wider query a head
-        shaped = not self.extended and out_scale == 1.0 and ops.attn_shaped_supported(
+        shaped = ops.attn_shaped_supported(
             proj.dtype, self.num_kv_heads, self.head_dim, self.vdim, cache.page_size, proj.stride(0), self.head_mix)
         mixed_q = None
         if shaped and self.head_mix:
@@ -256,7 +256,7 @@ class ModulatedAttention(Mixer):
             head_mix=self.mix if mixed_q is not None else None,
             mix_temperature=self.temperature if (mixed_q is not None or fold) else None, mixed_q=mixed_q)
         if shaped:
-            self.attend_shaped(attn, proj, mixed_q, step, cache, None if fold else self.temperature)
+            self.attend_shaped(attn, proj, mixed_q, step, cache, None if fold else self.temperature, out_scale)
         else:
             self.attend(attn, proj, step, cache, out_scale)
 
@@ -276,7 +276,7 @@ class ModulatedAttention(Mixer):
                                 query_temperature=self.query_temperature, gate_channels=self.channel_gate,
                                 out_scale=out_scale)
 
-    def attend_shaped(self, out, proj, mixed_q, step, cache, temperature) -> None:
+    def attend_shaped(self, out, proj, mixed_q, step, cache, temperature, out_scale: float = 1.0) -> None:
         """Tensor cores.  Single-token entries come first in a step: their keys are cut into parts of one or more
         stages of 64 keys, a CTA each (as many parts as the step's single tokens leave SMs for, so the order of a
         position's sums depends on how many tokens decode together, within rounding); the portions of prompts after
@@ -291,6 +291,9 @@ class ModulatedAttention(Mixer):
                 self.mask_size, self.sink, self.scale, step.status)
         head = (out, q, q.stride(0), mixed_q is not None, self._gate(proj), temperature, cache.k, cache.v,
                 cache.block_table)
+        more = dict(sink_values=self.sink_w, distance_bias=self.bias_by_distance, keep_first=self.keep_first,
+                    softcap=self.softcap, query_temperature=self.query_temperature, gate_channels=self.channel_gate,
+                    out_scale=out_scale)
         if n_single > 0:
             if self.mask == "causal":
                 stages = (int(step.max_kv_len) + 63) // 64 + 1
@@ -303,8 +306,9 @@ class ModulatedAttention(Mixer):
             span = (stages + want - 1) // want
             nsplit = (stages + span - 1) // span
             ops.attn_shaped(*head, step.cu_q, step.ctx_len, step.req_slot, n_single, n_single * ((group + 127) // 128),
-                            *tail, nsplit=nsplit, span=span)
+                            *tail, nsplit=nsplit, span=span, **more)
         if (n_rest > 0 and mixed_q is None and temperature is None and not self.sink and self.vdim == self.head_dim
+                and not self.extended and out_scale == 1.0
                 and self.mask in ("causal", "window") and ops.TC_ENABLED
                 and ops.attn_prefill_tc_supported(proj.dtype, self.head_dim, cache.page_size, proj.stride(0), group)):
             window = self.mask_size if self.mask == "window" else None
@@ -332,7 +336,7 @@ class ModulatedAttention(Mixer):
                 blocks = step.scratch[key] = ops.attn_shaped_blocks(
                     (len(e.tokens) for e in step.entries[n_single:]), group)
             ops.attn_shaped(*head, step.cu_q[n_single:], step.ctx_len[n_single:], step.req_slot[n_single:], n_rest,
-                            blocks, *tail)
+                            blocks, *tail, **more)
 
 
 register_part("mixer", "modulated_attention", ModulatedAttention)

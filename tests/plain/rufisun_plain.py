@@ -274,9 +274,14 @@ def dense_ff(u, w, p):
     return torch.relu(u @ w[p + "up"].T) ** 2 @ w[p + "down"].T
 
 
-def routed_ff(u, mlp, w, p):
+def routed_ff(u, mlp, w, p, margins=None):
+    """``margins`` (a list) receives, a token, how far the last chosen expert's score is above the first one not
+    chosen (infinite if all are chosen): where that is tiny, rounding may choose otherwise."""
     E, top = int(mlp["router"]["experts"]), int(mlp["router"]["top"])
     s = sigmoid(u @ w[p + "router"].T)                                    # [T, E]
+    if margins is not None:
+        ordered = torch.sort(s, dim=-1, descending=True).values
+        margins.append(ordered[:, top - 1] - ordered[:, top] if top < E else torch.full((u.shape[0],), math.inf, dtype=F))
     out = torch.zeros_like(u)
     for t in range(u.shape[0]):
         order = sorted(range(E), key=lambda e: (-float(s[t, e]), e))[:top]
@@ -287,16 +292,18 @@ def routed_ff(u, mlp, w, p):
     return out
 
 
-def feed_forward(u, mlp, w, p):
-    return dense_ff(u, w, p) if mlp["kind"] == "dense" else routed_ff(u, mlp, w, p)
+def feed_forward(u, mlp, w, p, margins=None):
+    return dense_ff(u, w, p) if mlp["kind"] == "dense" else routed_ff(u, mlp, w, p, margins)
 
 
 # --------------------------------------------------------------------------
 # the model
 # --------------------------------------------------------------------------
 
-def forward(cfg: Mapping, w: Mapping[str, torch.Tensor], tokens: List[int], layers_out: Optional[list] = None):
-    """Logits [T, vocab] of one whole sequence.  ``layers_out``: receives the residual after every layer."""
+def forward(cfg: Mapping, w: Mapping[str, torch.Tensor], tokens: List[int], layers_out: Optional[list] = None,
+            margins: Optional[list] = None):
+    """Logits [T, vocab] of one whole sequence.  ``layers_out``: receives the residual after every layer;
+    ``margins``: every routed layer's margins (see ``routed_ff``)."""
     eps = float(cfg["norm"]["eps"])
     ids = torch.tensor(tokens, dtype=torch.long)
     pos = torch.arange(len(tokens))
@@ -305,7 +312,7 @@ def forward(cfg: Mapping, w: Mapping[str, torch.Tensor], tokens: List[int], laye
         p = f"l{i}."
         x = x + MIXERS[layer["type"]](tanh_norm(x, w, p + "norm1"), pos, layer["mixer"], w, p + "mix.", eps)
         if layer.get("mlp") is not None:
-            x = x + feed_forward(tanh_norm(x, w, p + "norm2"), layer["mlp"], w, p + "mlp.")
+            x = x + feed_forward(tanh_norm(x, w, p + "norm2"), layer["mlp"], w, p + "mlp.", margins)
         if layers_out is not None:
             layers_out.append(x.clone())
     return tanh_norm(x, w, "final.norm") @ w["embed"].T
