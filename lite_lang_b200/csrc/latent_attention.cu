@@ -95,6 +95,9 @@ latent_prepare_kernel(const T* __restrict__ proj, long proj_stride, int q_off, i
 #define LA_WARPS 4
 #define LA_GH 8
 #define LA_MAX_R 512
+#define LA_PIPE 18      // 16-byte pieces of a tile a thread may hold: rows of up to 576 bfloat16 numbers
+// floats from one row of a tile in shared memory to the next
+__host__ __device__ static inline int la_pitch(int KD) { return (KD & 3) == 0 ? ((KD + 27) / 32) * 32 + 4 : KD + 1; }
 
 // q: [tokens, H, R + r] of T (latent-space queries, then the rotated part); cache: one plane
 // [pages, 1, page_size, R + r]; out: [tokens, H, R] of T.  `first` is the first token of the launch.
@@ -106,7 +109,7 @@ latent_attention_kernel(T* __restrict__ out, const T* __restrict__ q, const T* _
                         int r, int page_size, int num_pages, int window, float scale, int* status,
                         int tiles_per_split, float* __restrict__ part_acc, float* __restrict__ part_ml,
                         const float* __restrict__ sink) {
-  extern __shared__ float smem[];
+  extern __shared__ __align__(16) float smem[];
   __shared__ long base_s[LA_TK];
   LL_PDL_TRIGGER();
   LL_PDL_WAIT();
@@ -116,8 +119,12 @@ latent_attention_kernel(T* __restrict__ out, const T* __restrict__ q, const T* _
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int KD = R + r;
   float* qs = smem;                         // [LA_GH][KD]
-  float* ks = qs + LA_GH * KD;              // [LA_TK][KD + 1]
-  float* ps = ks + LA_TK * (KD + 1);        // [LA_TK][LA_GH]
+  // a row of the tile is KP floats apart.  Rows whose width is a multiple of 4 are read four numbers at a time:
+  // KP = 4 mod 32 then, so that the 16-byte reads of a quarter warp (lane = key) meet 32 different banks
+  const bool v4 = (KD & 3) == 0;
+  const int KP = la_pitch(KD);
+  float* ks = qs + LA_GH * KD;              // [LA_TK][KP]
+  float* ps = ks + LA_TK * KP;              // [LA_TK][LA_GH]
   float* alpha_s = ps + LA_GH * LA_TK;      // [LA_GH]
   float* l_s = alpha_s + LA_GH;             // [LA_GH]
 
@@ -158,13 +165,54 @@ latent_attention_kernel(T* __restrict__ out, const T* __restrict__ q, const T* _
   constexpr int VEC = 16 / (int)sizeof(T);
   const bool vec_ok = (KD % VEC) == 0 && ((uintptr_t)cache % 16) == 0;
 
+  // The rows of a tile come through registers a tile ahead where the pieces fit (16-byte pieces, at most LA_PIPE a
+  // thread): every thread asks for all its pieces of the next tile before it works on this one, so a CTA has a
+  // whole tile in flight instead of four pieces a thread, and the wait lies under the arithmetic.
+  const int vpr = KD / VEC;
+  const bool piped = vec_ok && LA_TK * vpr <= LA_PIPE * LA_THREADS;
+  uint4 raw[LA_PIPE];
+  auto ask = [&](int tile0) {
+#pragma unroll
+    for (int u = 0; u < LA_PIPE; ++u) {
+      const int i = tid + u * LA_THREADS;
+      raw[u] = make_uint4(0, 0, 0, 0);
+      if (i < LA_TK * vpr) {
+        const int row = i / vpr;
+        const int pos = tile0 + row;
+        if (pos >= lo && pos <= p) {
+          const int page = bt[pos / page_size];
+          if (page < 0 || page >= num_pages) set_status(status, LL_ERR_PAGE_RANGE);
+          else raw[u] = *reinterpret_cast<const uint4*>(cache + ((long)page * page_size + (pos % page_size)) * KD +
+                                                        (size_t)(i - row * vpr) * VEC);
+        }
+      }
+    }
+  };
+  auto put = [&]() {
+#pragma unroll
+    for (int u = 0; u < LA_PIPE; ++u) {
+      const int i = tid + u * LA_THREADS;
+      if (i < LA_TK * vpr) {
+        const T* e = reinterpret_cast<const T*>(&raw[u]);
+        float* dst = ks + (i / vpr) * KP + (i % vpr) * VEC;
+#pragma unroll
+        for (int x = 0; x < VEC; ++x) dst[x] = to_f32<T>(e[x]);
+      }
+    }
+  };
   int tile_begin = (lo / LA_TK) * LA_TK, tile_end = p;      // first positions of the first and (at most) last tile
   if (nsplit > 1) {
     tile_begin += split * tiles_per_split * LA_TK;
     tile_end = min(p, tile_begin + (tiles_per_split - 1) * LA_TK);
   }
+  if (piped && tile_begin <= tile_end) ask(tile_begin);
   for (int tile0 = tile_begin; tile0 <= tile_end; tile0 += LA_TK) {
     __syncthreads();
+    if (piped) {
+      put();
+      __syncthreads();
+      if (tile0 + LA_TK <= tile_end) ask(tile0 + LA_TK);
+    } else {
     if (tid < LA_TK) {
       const int pos = tile0 + tid;
       long base = -1;
@@ -195,7 +243,7 @@ latent_attention_kernel(T* __restrict__ out, const T* __restrict__ q, const T* _
           const int i = i0 + u * LA_THREADS;
           if (i < total) {
             const T* e = reinterpret_cast<const T*>(&v[u]);
-            float* dst = ks + (i / vpr) * (KD + 1) + (i % vpr) * VEC;
+            float* dst = ks + (i / vpr) * KP + (i % vpr) * VEC;
 #pragma unroll
             for (int x = 0; x < VEC; ++x) dst[x] = to_f32<T>(e[x]);
           }
@@ -217,11 +265,12 @@ latent_attention_kernel(T* __restrict__ out, const T* __restrict__ q, const T* _
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
           const int i = i0 + u * LA_THREADS;
-          if (i < total) ks[(i / KD) * (KD + 1) + i % KD] = v[u];
+          if (i < total) ks[(i / KD) * KP + i % KD] = v[u];
         }
       }
     }
     __syncthreads();
+    }
     {
       // scores and online softmax: warp w owns heads w and w + 4; lane = key
       const int pos = tile0 + lane;
@@ -229,11 +278,32 @@ latent_attention_kernel(T* __restrict__ out, const T* __restrict__ q, const T* _
       float s0 = 0.f, s1 = 0.f;
       const float* q0 = qs + warp * KD;
       const float* q1 = qs + (warp + LA_WARPS) * KD;
-      const float* kj = ks + lane * (KD + 1);
-      for (int c = 0; c < KD; ++c) {
-        const float kv = kj[c];
-        s0 = fmaf(q0[c], kv, s0);
-        s1 = fmaf(q1[c], kv, s1);
+      const float* kj = ks + lane * KP;
+      if (v4) {
+        const float4* q0v = reinterpret_cast<const float4*>(q0);
+        const float4* q1v = reinterpret_cast<const float4*>(q1);
+        const float4* kv4 = reinterpret_cast<const float4*>(kj);
+        float s0b = 0.f, s1b = 0.f;
+#pragma unroll 4
+        for (int c = 0; c < KD / 4; ++c) {
+          const float4 kv = kv4[c], a = q0v[c], b = q1v[c];
+          s0 = fmaf(a.x, kv.x, s0);
+          s0b = fmaf(a.y, kv.y, s0b);
+          s0 = fmaf(a.z, kv.z, s0);
+          s0b = fmaf(a.w, kv.w, s0b);
+          s1 = fmaf(b.x, kv.x, s1);
+          s1b = fmaf(b.y, kv.y, s1b);
+          s1 = fmaf(b.z, kv.z, s1);
+          s1b = fmaf(b.w, kv.w, s1b);
+        }
+        s0 += s0b;
+        s1 += s1b;
+      } else {
+        for (int c = 0; c < KD; ++c) {
+          const float kv = kj[c];
+          s0 = fmaf(q0[c], kv, s0);
+          s1 = fmaf(q1[c], kv, s1);
+        }
       }
 #pragma unroll
       for (int i = 0; i < LA_GH / LA_WARPS; ++i) {
@@ -254,7 +324,30 @@ latent_attention_kernel(T* __restrict__ out, const T* __restrict__ q, const T* _
       }
     }
     __syncthreads();
-    // accumulate P C: thread owns latent columns tid, tid + 128, ...; a key's number is read once for all heads
+    // accumulate P C: a thread owns latent columns 4 tid .. 4 tid + 3 (rows read four numbers at a time) or tid,
+    // tid + 128, ...; a key's number is read once for all heads
+    if (v4) {
+      if (4 * tid < R) {
+#pragma unroll
+        for (int g = 0; g < LA_GH; ++g)
+#pragma unroll
+          for (int c = 0; c < 4; ++c) acc[g][c] *= alpha_s[g];
+#pragma unroll 2
+        for (int j = 0; j < LA_TK; ++j) {
+          const float4 kv = *reinterpret_cast<const float4*>(ks + j * KP + 4 * tid);
+          const float4 pa = *reinterpret_cast<const float4*>(ps + j * LA_GH);
+          const float4 pb = *reinterpret_cast<const float4*>(ps + j * LA_GH + 4);
+          const float pw[LA_GH] = {pa.x, pa.y, pa.z, pa.w, pb.x, pb.y, pb.z, pb.w};
+#pragma unroll
+          for (int g = 0; g < LA_GH; ++g) {
+            acc[g][0] = fmaf(pw[g], kv.x, acc[g][0]);
+            acc[g][1] = fmaf(pw[g], kv.y, acc[g][1]);
+            acc[g][2] = fmaf(pw[g], kv.z, acc[g][2]);
+            acc[g][3] = fmaf(pw[g], kv.w, acc[g][3]);
+          }
+        }
+      }
+    } else
 #pragma unroll
     for (int c = 0; c < LA_MAX_R / LA_THREADS; ++c) {
       const int dd = tid + c * LA_THREADS;
@@ -263,7 +356,7 @@ latent_attention_kernel(T* __restrict__ out, const T* __restrict__ q, const T* _
         for (int g = 0; g < LA_GH; ++g) acc[g][c] *= alpha_s[g];
 #pragma unroll 4
         for (int j = 0; j < LA_TK; ++j) {
-          const float kv = ks[j * (KD + 1) + dd];
+          const float kv = ks[j * KP + dd];
           const float4 pa = *reinterpret_cast<const float4*>(ps + j * LA_GH);
           const float4 pb = *reinterpret_cast<const float4*>(ps + j * LA_GH + 4);
           acc[0][c] = fmaf(pa.x, kv, acc[0][c]);
@@ -293,7 +386,7 @@ latent_attention_kernel(T* __restrict__ out, const T* __restrict__ q, const T* _
   __syncthreads();
 #pragma unroll
   for (int c = 0; c < LA_MAX_R / LA_THREADS; ++c) {
-    const int dd = tid + c * LA_THREADS;
+    const int dd = v4 ? 4 * tid + c : tid + c * LA_THREADS;
     if (dd < R) {
 #pragma unroll
       for (int g = 0; g < LA_GH; ++g)
@@ -418,7 +511,7 @@ extern "C" int ll_latent_attention(int dtype, void* out, const void* q, const vo
   if (nsplit > 32 || (nsplit > 1 && (tiles_per_split < 1 || part_acc == nullptr || part_ml == nullptr)))
     return (int)cudaErrorInvalidValue;
   const int KD = R + r;
-  const size_t smem = sizeof(float) * ((size_t)LA_GH * KD + (size_t)LA_TK * (KD + 1) + LA_GH * LA_TK + 2 * LA_GH);
+  const size_t smem = sizeof(float) * ((size_t)LA_GH * KD + (size_t)LA_TK * la_pitch(KD) + LA_GH * LA_TK + 2 * LA_GH);
   dim3 grid(num_tokens, (H + LA_GH - 1) / LA_GH, nsplit);
   LL_DISPATCH_DTYPE(dtype, {
     if (smem > 48 * 1024)
