@@ -195,8 +195,15 @@ latent_attention_kernel(T* __restrict__ out, const T* __restrict__ q, const T* _
       if (i < LA_TK * vpr) {
         const T* e = reinterpret_cast<const T*>(&raw[u]);
         float* dst = ks + (i / vpr) * KP + (i % vpr) * VEC;
+        if (v4) {       // (rows start at multiples of 16 bytes then)
 #pragma unroll
-        for (int x = 0; x < VEC; ++x) dst[x] = to_f32<T>(e[x]);
+          for (int x = 0; x < VEC; x += 4)
+            *reinterpret_cast<float4*>(dst + x) =
+                make_float4(to_f32<T>(e[x]), to_f32<T>(e[x + 1]), to_f32<T>(e[x + 2]), to_f32<T>(e[x + 3]));
+        } else {
+#pragma unroll
+          for (int x = 0; x < VEC; ++x) dst[x] = to_f32<T>(e[x]);
+        }
       }
     }
   };
