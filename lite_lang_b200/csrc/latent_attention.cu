@@ -91,11 +91,13 @@ latent_prepare_kernel(const T* __restrict__ proj, long proj_stride, int q_off, i
 }
 
 #define LA_TK 32
-#define LA_THREADS 128
-#define LA_WARPS 4
+#define LA_THREADS 256
+#define LA_WARPS 8
+#define LA_HPW (LA_GH / LA_WARPS)     // heads a warp scores
+#define LA_CPT (LA_MAX_R / LA_THREADS) // latent columns a thread sums
 #define LA_GH 8
 #define LA_MAX_R 512
-#define LA_PIPE 18      // 16-byte pieces of a tile a thread may hold: rows of up to 576 bfloat16 numbers
+#define LA_PIPE 9       // 16-byte pieces of a tile a thread may hold: rows of up to 576 bfloat16 numbers
 // floats from one row of a tile in shared memory to the next
 __host__ __device__ static inline int la_pitch(int KD) { return (KD & 3) == 0 ? ((KD + 27) / 32) * 32 + 4 : KD + 1; }
 
@@ -279,44 +281,44 @@ latent_attention_kernel(T* __restrict__ out, const T* __restrict__ q, const T* _
     __syncthreads();
     }
     {
-      // scores and online softmax: warp w owns heads w and w + 4; lane = key
+      // scores and online softmax: warp w owns heads w, w + LA_WARPS, ...; lane = key
       const int pos = tile0 + lane;
       const bool valid = (pos >= lo && pos <= p);
-      float s0 = 0.f, s1 = 0.f;
-      const float* q0 = qs + warp * KD;
-      const float* q1 = qs + (warp + LA_WARPS) * KD;
+      float sh[LA_HPW];
       const float* kj = ks + lane * KP;
       if (v4) {
-        const float4* q0v = reinterpret_cast<const float4*>(q0);
-        const float4* q1v = reinterpret_cast<const float4*>(q1);
         const float4* kv4 = reinterpret_cast<const float4*>(kj);
-        float s0b = 0.f, s1b = 0.f;
+        float sa[LA_HPW], sb[LA_HPW], sc[LA_HPW], sd[LA_HPW];      // four sums side by side a head
+#pragma unroll
+        for (int i = 0; i < LA_HPW; ++i) sa[i] = sb[i] = sc[i] = sd[i] = 0.f;
 #pragma unroll 4
         for (int c = 0; c < KD / 4; ++c) {
-          const float4 kv = kv4[c], a = q0v[c], b = q1v[c];
-          s0 = fmaf(a.x, kv.x, s0);
-          s0b = fmaf(a.y, kv.y, s0b);
-          s0 = fmaf(a.z, kv.z, s0);
-          s0b = fmaf(a.w, kv.w, s0b);
-          s1 = fmaf(b.x, kv.x, s1);
-          s1b = fmaf(b.y, kv.y, s1b);
-          s1 = fmaf(b.z, kv.z, s1);
-          s1b = fmaf(b.w, kv.w, s1b);
+          const float4 kv = kv4[c];
+#pragma unroll
+          for (int i = 0; i < LA_HPW; ++i) {
+            const float4 a = reinterpret_cast<const float4*>(qs + (warp + i * LA_WARPS) * KD)[c];
+            sa[i] = fmaf(a.x, kv.x, sa[i]);
+            sb[i] = fmaf(a.y, kv.y, sb[i]);
+            sc[i] = fmaf(a.z, kv.z, sc[i]);
+            sd[i] = fmaf(a.w, kv.w, sd[i]);
+          }
         }
-        s0 += s0b;
-        s1 += s1b;
+#pragma unroll
+        for (int i = 0; i < LA_HPW; ++i) sh[i] = (sa[i] + sb[i]) + (sc[i] + sd[i]);
       } else {
+#pragma unroll
+        for (int i = 0; i < LA_HPW; ++i) sh[i] = 0.f;
         for (int c = 0; c < KD; ++c) {
           const float kv = kj[c];
-          s0 = fmaf(q0[c], kv, s0);
-          s1 = fmaf(q1[c], kv, s1);
+#pragma unroll
+          for (int i = 0; i < LA_HPW; ++i) sh[i] = fmaf(qs[(warp + i * LA_WARPS) * KD + c], kv, sh[i]);
         }
       }
 #pragma unroll
-      for (int i = 0; i < LA_GH / LA_WARPS; ++i) {
+      for (int i = 0; i < LA_HPW; ++i) {
         const int g = warp + i * LA_WARPS;
         if (g < hc) {
-          const float s = valid ? (i == 0 ? s0 : s1) * scale : -INFINITY;
+          const float s = valid ? sh[i] * scale : -INFINITY;
           const float m_new = fmaxf(m_run[i], warp_max(s));
           const float pj = valid ? expf(s - m_new) : 0.f;
           const float alpha = expf(m_run[i] - m_new);
@@ -331,17 +333,18 @@ latent_attention_kernel(T* __restrict__ out, const T* __restrict__ q, const T* _
       }
     }
     __syncthreads();
-    // accumulate P C: a thread owns latent columns 4 tid .. 4 tid + 3 (rows read four numbers at a time) or tid,
-    // tid + 128, ...; a key's number is read once for all heads
+    // accumulate P C: a thread owns LA_CPT neighbouring latent columns (rows read that many numbers at a time) or
+    // columns tid, tid + LA_THREADS, ...; a key's number is read once for all heads
     if (v4) {
-      if (4 * tid < R) {
+      static_assert(LA_CPT == 2, "the vector path reads two columns a thread");
+      if (LA_CPT * tid < R) {
 #pragma unroll
         for (int g = 0; g < LA_GH; ++g)
 #pragma unroll
-          for (int c = 0; c < 4; ++c) acc[g][c] *= alpha_s[g];
-#pragma unroll 2
+          for (int c = 0; c < LA_CPT; ++c) acc[g][c] *= alpha_s[g];
+#pragma unroll 4
         for (int j = 0; j < LA_TK; ++j) {
-          const float4 kv = *reinterpret_cast<const float4*>(ks + j * KP + 4 * tid);
+          const float2 kv = *reinterpret_cast<const float2*>(ks + j * KP + LA_CPT * tid);
           const float4 pa = *reinterpret_cast<const float4*>(ps + j * LA_GH);
           const float4 pb = *reinterpret_cast<const float4*>(ps + j * LA_GH + 4);
           const float pw[LA_GH] = {pa.x, pa.y, pa.z, pa.w, pb.x, pb.y, pb.z, pb.w};
@@ -349,8 +352,6 @@ latent_attention_kernel(T* __restrict__ out, const T* __restrict__ q, const T* _
           for (int g = 0; g < LA_GH; ++g) {
             acc[g][0] = fmaf(pw[g], kv.x, acc[g][0]);
             acc[g][1] = fmaf(pw[g], kv.y, acc[g][1]);
-            acc[g][2] = fmaf(pw[g], kv.z, acc[g][2]);
-            acc[g][3] = fmaf(pw[g], kv.w, acc[g][3]);
           }
         }
       }
@@ -393,7 +394,7 @@ latent_attention_kernel(T* __restrict__ out, const T* __restrict__ q, const T* _
   __syncthreads();
 #pragma unroll
   for (int c = 0; c < LA_MAX_R / LA_THREADS; ++c) {
-    const int dd = v4 ? 4 * tid + c : tid + c * LA_THREADS;
+    const int dd = v4 ? LA_CPT * tid + c : tid + c * LA_THREADS;
     if (dd < R) {
 #pragma unroll
       for (int g = 0; g < LA_GH; ++g)

@@ -45,7 +45,9 @@ ssd_prepare_kernel(const T* __restrict__ proj, long proj_stride, int x_off, int 
   }
   const int i = t - cu_q[e];                     // the token's place in its entry's portion
   const float* tail = state + (size_t)slot * state_stride + tail_off;
-  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+  // (the channels are shared out over gridDim.y blocks a token: with few tokens a block a token would leave the
+  // device to a handful of blocks, each a chain of its channels' loads)
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
     float acc = conv_b ? conv_b[c] : 0.f;
     for (int j = 0; j < taps; ++j) {
       const int back = taps - 1 - j;             // tap j weighs the input `back` positions before the token
@@ -56,6 +58,7 @@ ssd_prepare_kernel(const T* __restrict__ proj, long proj_stride, int x_off, int 
     }
     xbc[(size_t)t * C + c] = ssd_silu(acc);
   }
+  if (blockIdx.y != 0) return;
   for (int h = threadIdx.x; h < H; h += blockDim.x) {
     const float dt = ssd_softplus(to_f32<T>(proj[(size_t)t * proj_stride + dt_off + h]) + dt_bias[h]);
     dt_out[(size_t)t * H + h] = dt;
@@ -146,13 +149,17 @@ extern "C" int ll_ssd_prepare(int dtype, const void* proj, long proj_stride, int
                               cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   if (C <= 0 || H <= 0 || taps < 1) return (int)cudaErrorInvalidValue;
+  // blocks a token: as many as give a few hundred blocks in all, at most one a 256 channels
+  int by = (C + 255) / 256;
+  const int want = (296 + num_tokens - 1) / num_tokens;
+  by = by < want ? by : want;
   LL_DISPATCH_DTYPE(dtype, {
-    ll_launch(ssd_prepare_kernel<T>, dim3(num_tokens), dim3(256), 0, stream, (const T*)proj, proj_stride, x_off, dt_off,
+    ll_launch(ssd_prepare_kernel<T>, dim3(num_tokens, by), dim3(256), 0, stream, (const T*)proj, proj_stride, x_off, dt_off,
               conv_w, conv_b, A_log, dt_bias, (const float*)state, state_stride, tail_off, num_slots, token_req, cu_q,
               req_slot, xbc, dt_out, decay_out, C, H, taps, status);
     if (taps > 1 && write_state) {
-      const int by = (C + 255) / 256;
-      ll_launch(ssd_conv_update_kernel<T>, dim3(num_entries, by < 8 ? by : 8), dim3(256), 0, stream, (const T*)proj,
+      const int bu = (C + 255) / 256;
+      ll_launch(ssd_conv_update_kernel<T>, dim3(num_entries, bu < 8 ? bu : 8), dim3(256), 0, stream, (const T*)proj,
                 proj_stride, x_off, state, state_stride, tail_off, num_slots, cu_q, req_slot, C, taps);
     }
   });
