@@ -44,7 +44,7 @@ LIBRARIES: Dict[str, Tuple[Tuple[str, ...], Tuple[str, ...]]] = {
     "attn_tc": (("attention_prefill_tc.cu",), ()),
     "attn_mma_static": (("attention_mma_static.cu",), ()),
     "delta_rule": (("delta_rule.cu",), ()),
-    "latent_attn": (("latent_attention.cu",), ()),
+    "latent_attn": (("latent_attention.cu", "latent_attention_mma.cu"), ()),
     "moe": (("moe.cu",), ()),
     "streams": (("streams.cu",), ()),
     "linear_attn": (("linear_attention.cu",), ()),

@@ -509,6 +509,26 @@ extern "C" int ll_latent_prepare(int dtype, const void* proj, long proj_stride, 
   return LL_LAUNCH_RESULT();
 }
 
+// (latent_attention_mma.cu: the same work on tensor cores, for the sizes it takes)
+extern "C" int ll_latent_attention_mma_ok(int R, int r);
+extern "C" int ll_latent_attention_mma(void* out, const void* q, const void* cache, const int* block_table, int bt_stride,
+                                       const int* token_req, const int* req_slot, const int* positions, int first,
+                                       int num_tokens, int H, int R, int r, int page_size, int num_pages, int window,
+                                       float scale, int* status, int nsplit, int tiles_per_split, float* part_acc,
+                                       float* part_ml, const float* sink, cudaStream_t stream);
+static bool la_mma_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("LITE_LANG_B200_LATENT_MMA");
+    v = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
+}
+// Heads a CTA takes for these sizes: 16 on the tensor-core kernel, 8 on the other.
+extern "C" int ll_latent_attention_heads(int dtype, int R, int r) {
+  return (dtype == LL_DTYPE_BF16 && la_mma_enabled() && ll_latent_attention_mma_ok(R, r)) ? 16 : LA_GH;
+}
+
 extern "C" int ll_latent_attention(int dtype, void* out, const void* q, const void* cache, const int* block_table,
                                    int bt_stride, const int* token_req, const int* req_slot, const int* positions,
                                    int first, int num_tokens, int H, int R, int r, int page_size, int num_pages,
@@ -519,6 +539,16 @@ extern "C" int ll_latent_attention(int dtype, void* out, const void* q, const vo
   if (nsplit > 32 || (nsplit > 1 && (tiles_per_split < 1 || part_acc == nullptr || part_ml == nullptr)))
     return (int)cudaErrorInvalidValue;
   const int KD = R + r;
+  if (ll_latent_attention_heads(dtype, R, r) == 16 && ((uintptr_t)cache % 16) == 0 && ((uintptr_t)q % 16) == 0) {
+    const int rc = ll_latent_attention_mma(out, q, cache, block_table, bt_stride, token_req, req_slot, positions, first,
+                                           num_tokens, H, R, r, page_size, num_pages, window, scale, status, nsplit,
+                                           tiles_per_split, part_acc, part_ml, sink, stream);
+    if (rc != 0 || nsplit == 1) return rc;
+    const int pairs = num_tokens * H;
+    ll_launch(latent_merge_kernel<bf16>, dim3(pairs), dim3(128), 0, stream, (bf16*)out + (size_t)first * H * R,
+              (const float*)part_acc, (const float*)part_ml, pairs, R, nsplit, sink, H);
+    return LL_LAUNCH_RESULT();
+  }
   const size_t smem = sizeof(float) * ((size_t)LA_GH * KD + (size_t)LA_TK * la_pitch(KD) + LA_GH * LA_TK + 2 * LA_GH);
   dim3 grid(num_tokens, (H + LA_GH - 1) / LA_GH, nsplit);
   LL_DISPATCH_DTYPE(dtype, {

@@ -1228,6 +1228,14 @@ def latent_attention(out: torch.Tensor, q_full: torch.Tensor, cache: torch.Tenso
         _ptr(sink), _stream())
 
 
+def latent_attention_heads(dtype: torch.dtype, R: int, r: int) -> int:
+    """Heads a CTA of ``latent_attention`` takes for these sizes (16 on tensor cores: bfloat16, R + r a multiple of
+    16, R a multiple of 32; else 8): what a plan of the parts counts its CTAs with."""
+    if dtype not in _DT:
+        return 8
+    return int(load_library("latent_attn").fn("ll_latent_attention_heads")(c_int(_DT[dtype]), c_int(R), c_int(r)))
+
+
 def latent_gather(dst: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, slot: int, lo: int, page_size: int,
                   status: Optional[torch.Tensor], first: Optional[int] = None, last: Optional[int] = None) -> None:
     """dst [n, width]: row j = the cached row of position lo + j of the request in ``slot``, for positions

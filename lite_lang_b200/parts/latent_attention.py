@@ -154,14 +154,16 @@ class LatentAttention(Mixer):
         return ops.linear(heads, self.w_o)
 
     def _splits(self, n, step, device):
-        """How many CTAs share a query's keys, and how many tiles of 32 positions each takes: few queries with
+        """How many CTAs share a query's keys (a CTA takes a query's 8 heads, 16 on tensor cores), and how many tiles
+        of 32 positions each takes: few queries with
         many keys (decode steps) are spread until the CTAs fill the device about twice (a tile is a chain of
         latencies, so a CTA with one or two tiles beats fewer CTAs with more).
         The plan is made for the longest run of keys any query of the step may see (a captured step: of its class
         of context lengths), so it does not depend on what else is in the batch beyond that bound."""
         longest = step.max_kv_len if self.window is None else min(step.max_kv_len, self.window)
         tiles = (longest + 31) // 32 + 1                       # (a run that starts inside a tile touches one more)
-        ctas = n * ((self.H + 7) // 8)
+        group = ops.latent_attention_heads(self.w_o.dtype, self.R, self.r)
+        ctas = n * ((self.H + group - 1) // group)
         nsplit = max(1, min(tiles, (2 * ops.sm_count(device)) // max(1, ctas), 16))
         return nsplit, (tiles + nsplit - 1) // nsplit
 

@@ -503,6 +503,68 @@ def test_an_aimed_query_reads_its_key_inside_an_edge_and_not_the_one_outside():
 
 @gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,R,r,ps", [(12, 512, 32, 16), (4, 64, 16, 16), (28, 128, 16, 8), (17, 96, 32, 4), (3, 37, 6, 4),
+                                      (1, 32, 0, 16), (16, 256, 64, 64)])
+def test_latent_space_attention_with_a_sink_whole_and_in_parts(dtype, H, R, r, ps):
+    """Single tokens and a short portion of several requests against cached rows in scattered pages (the others
+    NaN), without and with a window, the keys whole or cut into parts that a second kernel merges, with a sink a
+    head: against the formula itself.  The sizes with R + r a multiple of 16 and R of 32 run on tensor cores in
+    bfloat16; one query is aimed at a key hundreds of positions back."""
+    from lite_lang_b200 import ops
+    g = torch.Generator().manual_seed(H * 1000 + R)
+    rng = np.random.default_rng(R)
+    KD = R + r
+    lens, new = [300, 41, 97, 520], [1, 5, 1, 1]
+    rows = [(torch.randn(n, KD, generator=g) * 0.5).to(dtype).float() for n in lens]
+    qs = [(torch.randn(c, H, KD, generator=g) * 0.3).to(dtype).float() for c in new]
+    qs[3][0, :, :] = 40.0 * rows[3][7] / rows[3][7].norm()               # aimed far back: a score of 20 there
+    qs = [x.to(dtype).float() for x in qs]
+    n_pages = sum((n + ps - 1) // ps for n in lens) + 3
+    order = rng.permutation(n_pages)
+    pool = torch.full((n_pages, 1, ps, KD), float("nan"), dtype=dtype)
+    bt = torch.full((4, max((n + ps - 1) // ps for n in lens)), -1, dtype=torch.int32)
+    at = 0
+    for i, k in enumerate(rows):
+        for j in range(len(k)):
+            if bt[i, j // ps] < 0:
+                bt[i, j // ps] = int(order[at])
+                at += 1
+            pool[bt[i, j // ps], 0, j % ps] = k[j].to(dtype)
+    step = _step(new, [n - c for n, c in zip(lens, new)], [0, 1, 2, 3])
+    q = torch.cat(qs).to(dtype).to(dev()).contiguous()
+    sink = torch.randn(H, generator=g) + 1.0
+    scale = 1.0 / math.sqrt(KD)
+    n_tok = sum(new)
+    for window in (None, 64):
+        want = []
+        for i in range(4):
+            T, c = lens[i], new[i]
+            K = rows[i].double()
+            for a in range(c):
+                p = T - c + a
+                lo = 0 if window is None else max(0, p - window + 1)
+                s = (qs[i][a].double() @ K[lo:p + 1].T) * scale                                   # [H, keys]
+                m = torch.maximum(s.max(-1, keepdim=True).values, sink.double()[:, None])
+                e = torch.exp(s - m)
+                w = e / (torch.exp(sink.double()[:, None] - m) + e.sum(-1, keepdim=True))
+                want.append(w @ K[lo:p + 1, :R])
+        want = torch.stack(want)
+        longest = max(lens) if window is None else window
+        tiles = (longest + 31) // 32 + 1
+        for nsplit in (1, 4, 16):
+            out = torch.full((n_tok, H, R), float("nan"), dtype=dtype, device=dev())
+            ops.latent_attention(out, q, pool.to(dev()), bt.to(dev()), step, 0, n_tok, H, R, r, ps, window, scale,
+                                 nsplit, (tiles + nsplit - 1) // nsplit, sink=sink.to(dev()))
+            assert int(step.status.item()) == 0
+            assert rel_err(out.float().cpu().numpy().reshape(n_tok, -1), want.numpy().reshape(n_tok, -1)) <= kernel_tol(dtype), \
+                (window, nsplit)
+        if window is None:       # the aimed query returns the latent it was aimed at
+            hit = out.float().cpu()[-1, 0]
+            assert float((hit - rows[3][7, :R]).abs().max()) < 0.1 * float(rows[3][7, :R].abs().max())
+
+
+@gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,Pd,N,G,taps,parts", [(6, 12, 20, 3, 3, 2), (4, 64, 64, 1, 4, 1), (4, 8, 16, 4, 1, 4),
                                                   (1, 24, 12, 1, 2, 1), (6, 48, 48, 2, 4, 2), (8, 64, 128, 2, 4, 1)])
 def test_state_space_pieces_in_portions_with_records_used_again(dtype, H, Pd, N, G, taps, parts):
