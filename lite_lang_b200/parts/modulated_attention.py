@@ -302,7 +302,9 @@ class ModulatedAttention(Mixer):
             # as many parts as give every SM a CTA, at most one part a stage and 32 parts: 8 tokens on 2 kv heads
             # with a window of 512 get 9 parts of one stage; 64 tokens one part each (and no join)
             ctas = n_single * self.num_kv_heads * ((group + 127) // 128)
-            want = max(1, min(32, ops.sm_count(out.device) // ctas))
+            # (without a window or chunks a token's walk is as long as its context: two CTAs an SM then)
+            slots = ops.sm_count(out.device) * (2 if self.mask == "causal" else 1)
+            want = max(1, min(32, slots // ctas))
             span = (stages + want - 1) // want
             nsplit = (stages + span - 1) // span
             ops.attn_shaped(*head, step.cu_q, step.ctx_len, step.req_slot, n_single, n_single * ((group + 127) // 128),
