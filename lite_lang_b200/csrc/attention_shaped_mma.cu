@@ -284,6 +284,18 @@ __global__ void __launch_bounds__(AS_THREADS) attn_shaped_kernel(const AttnShape
         if (key0 > w_hi || (key0 + 31 < w_lo && key0 >= keep)) continue;  // nothing of this piece is visible to the warp's rows
         const unsigned kt = k_base + buf * kt_bytes + (32 * sub) * kpitch;
         const unsigned vt = v_base + buf * VT_BYTES + (32 * sub) * VROW;
+        // the biases of this piece's scores are asked for before the products, whose time covers the table's latency
+        float bias_v[4][4];
+        if (p.rel) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+#pragma unroll
+            for (int x = 0; x < 4; ++x) {
+              const int i = x >> 1;
+              const int j = key0 + 8 * u + 2 * c + (x & 1);
+              bias_v[u][x] = __ldg(p.rel + (size_t)min(max(posr[i] - j, 0), p.nd - 1) * p.nh + headr[i]);
+            }
+        }
         // ---- S = Q K^T for 32 keys: four column tiles, two accumulation chains each ----
         float s_acc[4][4], s_odd[4][4];
 #pragma unroll
@@ -330,9 +342,9 @@ __global__ void __launch_bounds__(AS_THREADS) attn_shaped_kernel(const AttnShape
             const int i = x >> 1;
             float v = (s_acc[u][x] + s_odd[u][x]) * sc[i];
             if (p.cap_log2 > 0.f) v = p.cap_log2 * as_tanh(v * p.inv_cap_log2);
-            if (boundary || p.rel) {
+            if (p.rel) v = fmaf(bias_v[u][x], AS_LOG2E, v);
+            if (boundary) {
               const int j = key0 + 8 * u + 2 * c + (x & 1);
-              if (p.rel) v = fmaf(p.rel[(size_t)min(max(posr[i] - j, 0), p.nd - 1) * p.nh + headr[i]], AS_LOG2E, v);
               if (j > posr[i] || (j < lor[i] && j >= keep)) v = -INFINITY;
             }
             s_acc[u][x] = v;
