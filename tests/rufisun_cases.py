@@ -75,7 +75,7 @@ CASES = {
                         "mixer": _parallel((8, 2, 64, 64, 0.3, (0.25, 16), 30.0), (4, 64, 64, 1, 4, 1), 1.1, 0.8),
                         "mlp": _moe(8, 2, 64, 64)},
                        {"type": "attention", "mixer": _attention(8, 2, 64, 64, 0.25, 40, 16, 44, 16), "mlp": _dense(96)},
-                       {"type": "latent_attention", "mixer": _latent(4, 32, 16, 32, 64, 48, 0.35, 50000.0), "mlp": None},
+                       {"type": "latent_attention", "mixer": _latent(2, 48, 16, 32, 64, 48, 0.35, 30000.0), "mlp": None},
                        {"type": "attention", "mixer": _attention(2, 1, 128, 128, 0.15, 100, 32, 77, 3),
                         "mlp": _moe(4, 1, 32, 40)},
                    ]},

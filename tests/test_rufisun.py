@@ -195,14 +195,15 @@ def test_distance_buckets_and_frequencies_of_the_parts_are_the_plain_ones():
     from lite_lang_b200.config.spec import PartSpec
     from lite_lang_b200.parts import build_part
     from lite_lang_b200.parts.modulated_attention import distance_bucket
-    for B, D in ((32, 120), (12, 50), (7, 30), (2, 1000), (9, 64), (16, 40.5)):
+    for B, D in ((32, 100), (12, 50), (7, 30), (2, 1000), (9, 64), (16, 40.5)):
         assert [distance_bucket(n, B, D) for n in range(300)] == [P.distance_bucket(n, B, D) for n in range(300)]
     # the closed form: exact below B // 2, then logarithmic steps (17 is still in bucket 16, since
-    # 16 ln(17/16) / ln(7.5) < 1), capped at the last row, which D has reached; never decreasing
-    b = [P.distance_bucket(n, 32, 120) for n in range(200)]
-    assert b[:16] == list(range(16)) and b[16] == 16 and b[17] == 16 and b[100] == 30 and b[120] == 31 and b[199] == 31
+    # 16 ln(17/16) / ln(6.25) < 1; 64 = 16 x 4 lies 16 ln 4 / ln 6.25 = 12.1 steps on), capped at the last row,
+    # which D has reached; never decreasing
+    b = [P.distance_bucket(n, 32, 100) for n in range(200)]
+    assert b[:16] == list(range(16)) and b[16] == 16 and b[17] == 16 and b[64] == 28 and b[100] == 31 and b[199] == 31
     assert all(x <= y for x, y in zip(b, b[1:])) and set(b) == set(range(32))
-    for dims, base, sc in ((4, 10000.0, (4.0, 64, 32.0, 1.0)), (16, 50000.0, None), (4, 77.0, (2.0, 16, 2.0, 1.0))):
+    for dims, base, sc in ((4, 10000.0, (4.0, 64, 32.0, 1.0)), (16, 30000.0, None), (4, 77.0, (2.0, 16, 2.0, 1.0))):
         rot = {"dims": dims, "base": base}
         if sc:
             rot["scaling"] = dict(zip(("factor", "original", "fast", "slow"), sc))
@@ -414,7 +415,7 @@ def _attention_case(dtype, nh, nkv, hd, vd, ps, size, keep, buckets, far, cap, q
 
 ATTN_SHAPES = [  # nh, nkv, hd, vd, page size
     (6, 2, 24, 40, 4), (9, 1, 20, 28, 8), (1, 1, 36, 20, 4), (8, 2, 64, 64, 16), (4, 4, 128, 128, 16),
-    (2, 1, 128, 128, 64), (5, 5, 12, 20, 8), (8, 8, 96, 96, 16)]
+    (2, 1, 128, 128, 64), (5, 5, 12, 20, 8), (4, 2, 96, 80, 16)]
 
 
 @gpu
@@ -422,7 +423,7 @@ ATTN_SHAPES = [  # nh, nkv, hd, vd, page size
 @pytest.mark.parametrize("nh,nkv,hd,vd,ps", ATTN_SHAPES)
 def test_window_with_kept_tokens_distance_bias_sink_and_channel_gate(dtype, nh, nkv, hd, vd, ps):
     lens, new = [150, 61, 97, 300, 34], [40, 1, 97, 1, 5]
-    for size, keep, buckets, far in ((23, 5, 12, 50), (44, 16, 16, 40), (9, 0, 7, 30), (136, 20, 32, 120),
+    for size, keep, buckets, far in ((23, 5, 12, 50), (44, 16, 16, 40), (9, 0, 7, 30), (120, 24, 32, 200),
                                      (1000, 7, 2, 1000), (None, None, 9, 64)):
         _attention_case(dtype, nh, nkv, hd, vd, ps, size, keep, buckets, far, None, None, True, lens, new)
 
@@ -433,7 +434,7 @@ def test_window_with_kept_tokens_distance_bias_sink_and_channel_gate(dtype, nh, 
 def test_query_temperature_cap_and_sink(dtype, nh, nkv, hd, vd, ps):
     lens, new = [150, 61, 97, 300, 34], [40, 1, 97, 1, 5]
     for cap, q_temp, out_scale in ((5.0, (0.4, 7), 0.7), (30.0, (0.25, 16), 1.0), (None, None, 1.3), (2.0, (1.0, 1), 2.0),
-                                   (20.0, (0.3, 64), 1.2)):
+                                   (15.0, (0.35, 48), 1.1)):
         _attention_case(dtype, nh, nkv, hd, vd, ps, None, None, None, None, cap, q_temp, False, lens, new,
                         out_scale=out_scale)
 
@@ -446,7 +447,7 @@ SHAPED_SHAPES = [(8, 2, 64, 64, 16), (4, 4, 128, 128, 16), (2, 1, 128, 128, 64),
 def test_the_same_shapes_of_the_scores_on_tensor_cores(nh, nkv, hd, vd, ps):
     lens, new = [150, 61, 97, 300, 34, 700], [40, 1, 97, 1, 5, 1]
     dt = torch.bfloat16
-    for size, keep, buckets, far in ((23, 5, 12, 50), (44, 16, 16, 40), (136, 20, 32, 120), (100, 70, 32, 300),
+    for size, keep, buckets, far in ((23, 5, 12, 50), (44, 16, 16, 40), (120, 24, 32, 200), (100, 70, 32, 300),
                                      (1000, 7, 2, 1000), (None, None, 9, 64), (64, 64, 8, 64), (200, 130, 8, 64)):
         _attention_case(dt, nh, nkv, hd, vd, ps, size, keep, buckets, far, None, None, True, lens, new, kernel="shaped")
     for cap, q_temp, out_scale in ((5.0, (0.4, 7), 0.7), (30.0, (0.25, 16), 1.0), (None, None, 1.3), (2.0, (1.0, 1), 2.0)):
@@ -503,7 +504,7 @@ def test_an_aimed_query_reads_its_key_inside_an_edge_and_not_the_one_outside():
 
 @gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,R,r,ps", [(12, 512, 32, 16), (4, 64, 16, 16), (28, 128, 16, 8), (17, 96, 32, 4), (3, 37, 6, 4),
+@pytest.mark.parametrize("H,R,r,ps", [(12, 512, 32, 16), (4, 64, 16, 16), (28, 160, 16, 8), (17, 96, 32, 4), (3, 37, 6, 4),
                                       (1, 32, 0, 16), (16, 256, 64, 64)])
 def test_latent_space_attention_with_a_sink_whole_and_in_parts(dtype, H, R, r, ps):
     """Single tokens and a short portion of several requests against cached rows in scattered pages (the others
@@ -566,7 +567,7 @@ def test_latent_space_attention_with_a_sink_whole_and_in_parts(dtype, H, R, r, p
 @gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,Pd,N,G,taps,parts", [(6, 12, 20, 3, 3, 2), (4, 64, 64, 1, 4, 1), (4, 8, 16, 4, 1, 4),
-                                                  (1, 24, 12, 1, 2, 1), (6, 48, 48, 2, 4, 2), (8, 64, 128, 2, 4, 1)])
+                                                  (1, 24, 12, 1, 2, 1), (6, 40, 56, 2, 4, 3), (8, 64, 128, 2, 4, 1)])
 def test_state_space_pieces_in_portions_with_records_used_again(dtype, H, Pd, N, G, taps, parts):
     """Convolution with the record's tail, step sizes and decays, the scan and the gated norm, for three requests
     fed in portions of unequal sizes (down to one token, shorter than the taps) through records that held
